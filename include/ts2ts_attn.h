@@ -1,0 +1,100 @@
+/* libts2ts_attn -- C ABI of the sm_100a masked flash-attention path.
+ *
+ * The entry points replace, for TAGSeq2TAGSeq's attention hot path, what the
+ * reference reaches through two Python seams (it has no FFI of its own):
+ *   - the block_mask_creator callable injected into TS2TSTrainingModule
+ *     (model/modules/training_module.py:36-65,199-200), which ends in torch's
+ *     create_block_mask (model/graph_traversal/block_mask_creator.py:132-139,
+ *     model/graph_traversal/cross_doc_mask.py:359-366);
+ *   - the flex_attention symbol called by the attention module
+ *     (model/modules/layer.py:33; patched at generate.py:167-178).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its comment says "host";
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and
+ *     the call returns without synchronising (ts2ts_read_status synchronises);
+ *   - the caller owns every buffer; the library allocates no device memory;
+ *   - return value 0 = OK, < 0 = rejected arguments or launch failure (nothing
+ *     or only part of the work was enqueued; ts2ts_last_error_string() explains),
+ *     > 0 only from ts2ts_read_status = code recorded by a kernel whose bounded
+ *     wait ran out;
+ *   - tensors q, k, v, out, dout, dq, dk, dv are bf16 [B,H,T,D] with D in
+ *     {64, 128} contiguous and element strides {batch, head, token} given in
+ *     a host int64_t[3]; base pointers and byte strides are multiples of 16;
+ *   - the mask is
+ *         allowed(q, kv) = q >= kv  and  ( doc_ids[q] == doc_ids[kv]
+ *                          or  bit( link_bits[b, q_row_ids[q], :], kv_col_ids[kv] ) )
+ *     with a negative or out-of-range class granting nothing.  link_bits == NULL
+ *     is the reference's `doc_causal` mask; with link_bits it expresses
+ *     `cross_doc_link` (cross_doc_mask.py:348-357).  q_row_ids / kv_col_ids may
+ *     be NULL, meaning doc_ids are used as class numbers.
+ */
+#ifndef TS2TS_ATTN_H_
+#define TS2TS_ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TS2TS_TILE 128
+
+/* Library version (major*1000 + minor). */
+int ts2ts_version(void);
+
+/* Host string describing the last non-zero return on the calling thread. */
+const char* ts2ts_last_error_string(void);
+
+/* Size in bytes of the block plan for B sequences of T tokens (0 if B or T is invalid). */
+size_t ts2ts_plan_bytes(int B, int T);
+
+/* Integer pre-pass.  Fills `plan` (ts2ts_plan_bytes(B,T) bytes, 256-byte aligned), which the
+ * attention calls below read, from the per-token mask inputs:
+ *   doc_ids    int32[B,T]
+ *   q_row_ids  int32[B,T] or NULL     kv_col_ids int32[B,T] or NULL
+ *   link_bits  int64[B,R,W] or NULL   (bit c%64 of word c/64 of row r)
+ * Optional outputs (any may be NULL), NB = ceil(T/128), in the layout of torch's BlockMask
+ * that create_block_mask returns to the reference (torch/nn/attention/flex_attention.py:1207-1289):
+ *   state      uint8[B,NB,NB]   0 skip, 1 partial, 2 full, indexed [b, q tile, kv tile]
+ *   kv_cnt     int32[B,NB]      kv_idx     int32[B,NB,NB]   partial kv tiles of a q tile, ascending, then -1
+ *   full_cnt   int32[B,NB]      full_idx   int32[B,NB,NB]   full kv tiles
+ *   q_cnt      int32[B,NB]      q_idx      int32[B,NB,NB]   partial q tiles of a kv tile
+ *   full_q_cnt int32[B,NB]      full_q_idx int32[B,NB,NB]   full q tiles of a kv tile */
+int ts2ts_block_map(const int32_t* doc_ids, const int32_t* q_row_ids, const int32_t* kv_col_ids,
+                    const int64_t* link_bits, int B, int T, int R, int W, void* plan, size_t plan_bytes,
+                    uint8_t* state, int32_t* kv_cnt, int32_t* kv_idx, int32_t* full_cnt, int32_t* full_idx,
+                    int32_t* q_cnt, int32_t* q_idx, int32_t* full_q_cnt, int32_t* full_q_idx, void* stream);
+
+/* Forward: out = softmax(scale * q k^T + mask) v, lse = natural-log row sums, fp32 [B,H,T].
+ * A row with no allowed key gets out = 0 and lse = -inf.  Replaces the forward of
+ * flex_attention(q, k, v, block_mask=...) (torch/nn/attention/flex_attention.py:1468). */
+int ts2ts_attn_fwd(const void* q, const void* k, const void* v, const int64_t* q_strides, const int64_t* k_strides,
+                   const int64_t* v_strides, int B, int H, int T, int D, float scale, const int32_t* doc_ids,
+                   const int32_t* q_row_ids, const int32_t* kv_col_ids, const int64_t* link_bits, int R, int W,
+                   const void* plan, size_t plan_bytes, void* out, const int64_t* out_strides, float* lse, void* stream);
+
+/* Scratch size in bytes that ts2ts_attn_bwd needs. */
+size_t ts2ts_attn_bwd_workspace_bytes(int B, int H, int T, int D);
+
+/* Backward of the call above: given out, lse and dout computes dq, dk, dv (bf16, own strides).
+ * `workspace` is caller-owned scratch of ts2ts_attn_bwd_workspace_bytes() bytes, 256-byte aligned;
+ * its contents need not be preserved between calls.  Replaces the autograd backward of
+ * flex_attention (torch/_higher_order_ops/flex_attention.py:947-1075). */
+int ts2ts_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                   const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                   const int64_t* out_strides, const int64_t* dout_strides, int B, int H, int T, int D, float scale,
+                   const int32_t* doc_ids, const int32_t* q_row_ids, const int32_t* kv_col_ids,
+                   const int64_t* link_bits, int R, int W, const void* plan, size_t plan_bytes, void* dq, void* dk,
+                   void* dv, const int64_t* dq_strides, const int64_t* dk_strides, const int64_t* dv_strides,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* Waits for `stream`, then copies the plan's device status word to *status_out (host).
+ * 0 = every kernel that used this plan since the last ts2ts_block_map ran to completion. */
+int ts2ts_read_status(const void* plan, void* stream, int32_t* status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TS2TS_ATTN_H_ */

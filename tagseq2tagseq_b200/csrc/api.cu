@@ -1,0 +1,172 @@
+// extern "C" surface of libts2ts_attn.so: argument checks, then kernel launches on the caller's stream.
+// Declarations and the contract of every entry point are in include/ts2ts_attn.h.
+#include "../../include/ts2ts_attn.h"
+
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "plan.h"
+
+namespace ts2ts {
+cudaError_t launch_block_map(PlanView P, MaskArgs M, uint8_t* state_out, int32_t* kv_cnt, int32_t* kv_idx, int32_t* full_cnt,
+                             int32_t* full_idx, int32_t* q_cnt, int32_t* q_idx, int32_t* full_q_cnt, int32_t* full_q_idx,
+                             cudaStream_t stream);
+int launch_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int64_t* sq, const int64_t* sk,
+               const int64_t* sv, const int64_t* so, int B, int H, int T, int D, float scale, PlanView P, MaskArgs M,
+               cudaStream_t stream);
+size_t bwd_workspace_bytes(int B, int H, int T, int D);
+int launch_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse, const int64_t* sq,
+               const int64_t* sk, const int64_t* sv, const int64_t* so, const int64_t* sdo, int B, int H, int T, int D, float scale,
+               PlanView P, MaskArgs M, void* dq, void* dk, void* dv, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv,
+               void* workspace, cudaStream_t stream);
+}  // namespace ts2ts
+
+using namespace ts2ts;
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+constexpr int kMaxT = 1 << 20;
+
+bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+
+int check_shape(int B, int H, int T, int D) {
+  if (B <= 0 || H <= 0 || T <= 0) return fail(-1, "B, H and T must be positive (got B=%d H=%d T=%d)", B, H, T);
+  if (T > kMaxT) return fail(-1, "T=%d exceeds the supported maximum %d", T, kMaxT);
+  if (D != 64 && D != 128) return fail(-2, "head dimension must be 64 or 128 (got %d)", D);
+  if ((long long)B * H * ((T + kTile - 1) / kTile) > 0x7fffffffLL) return fail(-1, "too many tiles for one launch");
+  return 0;
+}
+
+int check_tensor(const char* name, const void* p, const int64_t* s) {
+  if (p == nullptr || s == nullptr) return fail(-3, "%s: null pointer", name);
+  if (!aligned(p, 16)) return fail(-4, "%s: base address must be 16-byte aligned", name);
+  for (int i = 0; i < 3; ++i)
+    if (s[i] <= 0 || (s[i] * 2) % 16 != 0) return fail(-5, "%s: stride %d = %lld elements is not a positive multiple of 8", name, i, (long long)s[i]);
+  return 0;
+}
+
+int check_mask(const int32_t* doc, const int64_t* link, int R, int W) {
+  if (doc == nullptr) return fail(-6, "doc_ids is null");
+  if (link != nullptr && (R <= 0 || W <= 0)) return fail(-6, "link_bits given with R=%d W=%d", R, W);
+  if (link == nullptr && (R != 0 || W != 0)) return fail(-6, "R and W must be 0 when link_bits is null");
+  return 0;
+}
+
+int check_plan(const void* plan, size_t plan_bytes, int B, int T) {
+  if (plan == nullptr || !aligned(plan, 256)) return fail(-7, "plan must be a 256-byte aligned device buffer");
+  if (plan_bytes < plan_layout(B, T).bytes) return fail(-7, "plan buffer too small: %zu < %zu", plan_bytes, plan_layout(B, T).bytes);
+  return 0;
+}
+
+MaskArgs mask_args(const int32_t* doc, const int32_t* row, const int32_t* col, const int64_t* link, int R, int W) {
+  MaskArgs m;
+  m.doc = doc;
+  m.row = row ? row : doc;
+  m.col = col ? col : doc;
+  m.link = link;
+  m.R = R;
+  m.W = W;
+  return m;
+}
+
+}  // namespace
+
+extern "C" {
+
+int ts2ts_version(void) { return 1000; }
+
+const char* ts2ts_last_error_string(void) { return g_err; }
+
+size_t ts2ts_plan_bytes(int B, int T) {
+  if (B <= 0 || T <= 0 || T > kMaxT) return 0;
+  return plan_layout(B, T).bytes;
+}
+
+int ts2ts_block_map(const int32_t* doc_ids, const int32_t* q_row_ids, const int32_t* kv_col_ids, const int64_t* link_bits, int B,
+                    int T, int R, int W, void* plan, size_t plan_bytes, uint8_t* state, int32_t* kv_cnt, int32_t* kv_idx,
+                    int32_t* full_cnt, int32_t* full_idx, int32_t* q_cnt, int32_t* q_idx, int32_t* full_q_cnt,
+                    int32_t* full_q_idx, void* stream) {
+  int r;
+  if (B <= 0 || T <= 0 || T > kMaxT) return fail(-1, "B and T must be positive, T <= %d (got B=%d T=%d)", kMaxT, B, T);
+  if ((r = check_mask(doc_ids, link_bits, R, W))) return r;
+  if ((r = check_plan(plan, plan_bytes, B, T))) return r;
+  PlanView P = plan_view(plan, B, T);
+  cudaError_t e = launch_block_map(P, mask_args(doc_ids, q_row_ids, kv_col_ids, link_bits, R, W), state, kv_cnt, kv_idx, full_cnt,
+                                   full_idx, q_cnt, q_idx, full_q_cnt, full_q_idx, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(-50, "block map launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+int ts2ts_attn_fwd(const void* q, const void* k, const void* v, const int64_t* q_strides, const int64_t* k_strides,
+                   const int64_t* v_strides, int B, int H, int T, int D, float scale, const int32_t* doc_ids,
+                   const int32_t* q_row_ids, const int32_t* kv_col_ids, const int64_t* link_bits, int R, int W, const void* plan,
+                   size_t plan_bytes, void* out, const int64_t* out_strides, float* lse, void* stream) {
+  int r;
+  if ((r = check_shape(B, H, T, D))) return r;
+  if (!(scale > 0.f)) return fail(-8, "scale must be positive");
+  if ((r = check_tensor("q", q, q_strides)) || (r = check_tensor("k", k, k_strides)) || (r = check_tensor("v", v, v_strides)) ||
+      (r = check_tensor("out", out, out_strides)))
+    return r;
+  if (lse == nullptr) return fail(-3, "lse: null pointer");
+  if ((r = check_mask(doc_ids, link_bits, R, W))) return r;
+  if ((r = check_plan(plan, plan_bytes, B, T))) return r;
+  PlanView P = plan_view(const_cast<void*>(plan), B, T);
+  r = launch_fwd(q, k, v, out, lse, q_strides, k_strides, v_strides, out_strides, B, H, T, D, scale, P,
+                 mask_args(doc_ids, q_row_ids, kv_col_ids, link_bits, R, W), static_cast<cudaStream_t>(stream));
+  if (r) return fail(r, "forward launch failed (code %d, CUDA: %s)", r, cudaGetErrorString(cudaPeekAtLastError()));
+  return 0;
+}
+
+size_t ts2ts_attn_bwd_workspace_bytes(int B, int H, int T, int D) {
+  if (B <= 0 || H <= 0 || T <= 0 || T > kMaxT || (D != 64 && D != 128)) return 0;
+  return bwd_workspace_bytes(B, H, T, D);
+}
+
+int ts2ts_attn_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                   const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides, const int64_t* out_strides,
+                   const int64_t* dout_strides, int B, int H, int T, int D, float scale, const int32_t* doc_ids,
+                   const int32_t* q_row_ids, const int32_t* kv_col_ids, const int64_t* link_bits, int R, int W, const void* plan,
+                   size_t plan_bytes, void* dq, void* dk, void* dv, const int64_t* dq_strides, const int64_t* dk_strides,
+                   const int64_t* dv_strides, void* workspace, size_t workspace_bytes, void* stream) {
+  int r;
+  if ((r = check_shape(B, H, T, D))) return r;
+  if (!(scale > 0.f)) return fail(-8, "scale must be positive");
+  if ((r = check_tensor("q", q, q_strides)) || (r = check_tensor("k", k, k_strides)) || (r = check_tensor("v", v, v_strides)) ||
+      (r = check_tensor("out", out, out_strides)) || (r = check_tensor("dout", dout, dout_strides)) ||
+      (r = check_tensor("dq", dq, dq_strides)) || (r = check_tensor("dk", dk, dk_strides)) || (r = check_tensor("dv", dv, dv_strides)))
+    return r;
+  if (lse == nullptr) return fail(-3, "lse: null pointer");
+  if ((r = check_mask(doc_ids, link_bits, R, W))) return r;
+  if ((r = check_plan(plan, plan_bytes, B, T))) return r;
+  if (workspace == nullptr || !aligned(workspace, 256)) return fail(-9, "workspace must be a 256-byte aligned device buffer");
+  if (workspace_bytes < bwd_workspace_bytes(B, H, T, D))
+    return fail(-9, "workspace too small: %zu < %zu", workspace_bytes, bwd_workspace_bytes(B, H, T, D));
+  PlanView P = plan_view(const_cast<void*>(plan), B, T);
+  r = launch_bwd(q, k, v, out, dout, lse, q_strides, k_strides, v_strides, out_strides, dout_strides, B, H, T, D, scale, P,
+                 mask_args(doc_ids, q_row_ids, kv_col_ids, link_bits, R, W), dq, dk, dv, dq_strides, dk_strides, dv_strides,
+                 workspace, static_cast<cudaStream_t>(stream));
+  if (r) return fail(r, "backward launch failed (code %d, CUDA: %s)", r, cudaGetErrorString(cudaPeekAtLastError()));
+  return 0;
+}
+
+int ts2ts_read_status(const void* plan, void* stream, int32_t* status_out) {
+  if (plan == nullptr || status_out == nullptr) return fail(-3, "null pointer");
+  cudaError_t e = cudaMemcpyAsync(status_out, plan, sizeof(int32_t), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
+  if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(-60, "status read failed: %s", cudaGetErrorString(e));
+  if (*status_out != 0) fail(*status_out, "a kernel gave up a bounded wait (code %d)", *status_out);
+  return 0;
+}
+
+}  // extern "C"
