@@ -1,0 +1,332 @@
+#!/usr/bin/env python
+"""Benchmark of the masked flash-attention hot path (block-map pre-pass + forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload = the 32k configuration the headline metric is quoted on: B=2, T=32768, H=16, D=128, bf16, swept over
+three masks (doc_causal, cross_doc_link with p=0.05 and p=0.3) on seeded synthetic packs (median 150 tokens,
+5 % of documents of 4k-8k tokens).  One step = for each mask: pre-pass, forward, backward.  The metric counts
+only unmasked FLOPs: 14 * D * H * N with N the exact number of allowed (q, kv) pairs.
+
+Prints ONE JSON line on rank 0.  Under torchrun every rank runs its own packs (seed + 1000 * rank); there is no
+collective on this path, so the multi-GPU number is the weak-scaling aggregate over independent replicas.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+B, T, H, D = 2, 32768, 16, 128
+MASKS = ["doc_causal", "link_p05", "link_p30"]
+SEED = 1003
+WORKLOAD = "attn_fwd_bwd_32k_mask_sweep"
+METRIC = "masked attn fwd+bwd TFLOP/s (unmasked FLOPs) at 32k"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return d["bf16_tflops"], d["hbm_gbs"], "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+        return self
+
+    def __exit__(self, *exc):
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return
+        time.sleep(0.25)
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0])); mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if sm:
+            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_workload(rank: int, device):
+    from tagseq2tagseq_b200 import synth
+    masks = []
+    for mi, name in enumerate(MASKS):
+        if WORKLOAD == "attn_fwd_bwd_16k_cross_doc_link":
+            packs = [synth.config2_pack(SEED + 1000 * rank + b) for b in range(B)]
+        else:
+            packs = [synth.config3_pack(SEED + 1000 * rank + 10 * mi + b, name) for b in range(B)]
+        doc_np, link_np = synth.stack_packs(packs)
+        n_pairs = sum(p.unmasked_pairs() for p in packs)
+        masks.append({"name": name, "doc": torch.from_numpy(doc_np).to(device),
+                      "link": None if link_np is None else torch.from_numpy(link_np).to(device),
+                      "doc_host": torch.from_numpy(doc_np).pin_memory(),
+                      "link_host": None if link_np is None else torch.from_numpy(link_np).pin_memory(),
+                      "pairs": n_pairs, "density": n_pairs / (B * T * T), "docs": [int(p.lengths.size) for p in packs]})
+    return masks
+
+
+def flops_of(pairs: int) -> float:
+    return 14.0 * D * H * pairs
+
+
+def run_ours(args, rank, world, device):
+    from tagseq2tagseq_b200 import _lib
+    from tagseq2tagseq_b200.attention import _attn_bwd, _attn_fwd
+    from tagseq2tagseq_b200.mask_spec import build_block_map, read_status
+
+    L = _lib.lib()
+    torch.manual_seed(SEED + rank)
+    masks = make_workload(rank, device)
+    q, k, v, do = (torch.randn(B, H, T, D, device=device, dtype=torch.float32).bfloat16() for _ in range(4))
+    scale = 1.0 / D ** 0.5
+    launches = [0]
+
+    def step_device():
+        for m in masks:
+            bm = build_block_map(m["doc"], m["link"])
+            out, lse = _attn_fwd(q, k, v, m["doc"], m["link"], None, None, bm.plan, scale)
+            _attn_bwd(q, k, v, out, do, lse, m["doc"], m["link"], None, None, bm.plan, scale)
+            launches[0] += 5 + 1 + 3  # pre-pass kernels, forward, backward (prep, main, convert)
+        return bm
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+
+    for _ in range(max(3, args.warmup)):
+        bm = step_device()
+    barrier()
+    if read_status(bm.plan) != 0:
+        raise RuntimeError("a kernel reported a bounded-wait timeout during warm-up")
+    launches[0] = 0
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(device.index) as clocks:
+        barrier()
+        ev0.record()
+        for _ in range(args.steps):
+            step_device()
+        ev1.record()
+        barrier()
+    ms = ev0.elapsed_time(ev1)
+    total_flops = sum(flops_of(m["pairs"]) for m in masks) * args.steps
+    n_launch = launches[0]
+
+    # ---- per-kernel timing (main forward / backward kernels) for the roofline, same inputs, after the timed region
+    L.ts2ts_profile_enable(1)
+    per_mask = []
+    fms, bms = ctypes.c_float(0), ctypes.c_float(0)
+    for m in masks:
+        f_list, b_list = [], []
+        for _ in range(max(3, min(args.steps, 10))):
+            bm = build_block_map(m["doc"], m["link"])
+            out, lse = _attn_fwd(q, k, v, m["doc"], m["link"], None, None, bm.plan, scale)
+            _attn_bwd(q, k, v, out, do, lse, m["doc"], m["link"], None, None, bm.plan, scale)
+            L.ts2ts_profile_last_ms(0, ctypes.byref(fms)); L.ts2ts_profile_last_ms(1, ctypes.byref(bms))
+            f_list.append(fms.value); b_list.append(bms.value)
+        per_mask.append({"mask": m["name"], "density": round(m["density"], 4), "fwd_ms": statistics.mean(f_list),
+                         "bwd_ms": statistics.mean(b_list), "fwd_tflops": 4.0 * D * H * m["pairs"] / statistics.mean(f_list) / 1e9,
+                         "bwd_tflops": 10.0 * D * H * m["pairs"] / statistics.mean(b_list) / 1e9})
+    L.ts2ts_profile_enable(0)
+    bwd_flops = sum(10.0 * D * H * m["pairs"] for m in masks) / len(masks)
+    bwd_ms = statistics.mean(p["bwd_ms"] for p in per_mask)
+    peak_tf, peak_hbm, peak_kind = measured_peaks()
+    achieved = sum(10.0 * D * H * m["pairs"] for m in masks) / sum(p["bwd_ms"] for p in per_mask) / 1e9
+
+    # ---- end to end: pinned host buffers in, results back to host, through the same entry points
+    hq, hk, hv, hdo = (x.cpu().pin_memory() for x in (q, k, v, do))
+    h_out, h_dq, h_dk, h_dv = (torch.empty((B, H, T, D), dtype=torch.bfloat16).pin_memory() for _ in range(4))
+    h_lse = torch.empty((B, H, T), dtype=torch.float32).pin_memory()
+    dq_, dk_, dv_, do_ = (torch.empty_like(q) for _ in range(4))
+
+    def step_e2e():
+        for m in masks:
+            dq_.copy_(hq, non_blocking=True); dk_.copy_(hk, non_blocking=True); dv_.copy_(hv, non_blocking=True)
+            do_.copy_(hdo, non_blocking=True)
+            doc = m["doc_host"].to(device, non_blocking=True)
+            link = None if m["link_host"] is None else m["link_host"].to(device, non_blocking=True)
+            bm = build_block_map(doc, link)
+            out, lse = _attn_fwd(dq_, dk_, dv_, doc, link, None, None, bm.plan, scale)
+            gq, gk, gv = _attn_bwd(dq_, dk_, dv_, out, do_, lse, doc, link, None, None, bm.plan, scale)
+            h_out.copy_(out, non_blocking=True); h_lse.copy_(lse, non_blocking=True)
+            h_dq.copy_(gq, non_blocking=True); h_dk.copy_(gk, non_blocking=True); h_dv.copy_(gv, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    step_e2e()
+    barrier()
+    ev0.record()
+    for _ in range(e2e_steps):
+        step_e2e()
+    ev1.record()
+    barrier()
+    e2e_ms = ev0.elapsed_time(ev1)
+    tens = B * H * T * D * 2
+    mask_bytes = sum(m["doc_host"].numel() * 4 + (0 if m["link_host"] is None else m["link_host"].numel() * 8) for m in masks)
+    h2d = 4 * tens * len(masks) + mask_bytes
+    d2h = (4 * tens + B * H * T * 4) * len(masks)
+
+    t_ms = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
+    fl = torch.tensor([total_flops, sum(flops_of(m["pairs"]) for m in masks) * e2e_steps], device=device, dtype=torch.float64)
+    if world > 1:
+        torch.distributed.all_reduce(t_ms, op=torch.distributed.ReduceOp.MAX)
+        torch.distributed.all_reduce(fl, op=torch.distributed.ReduceOp.SUM)
+    if rank != 0:
+        return
+    value = fl[0].item() / (t_ms[0].item() * 1e-3) / 1e12
+    e2e_value = fl[1].item() / (t_ms[1].item() * 1e-3) / 1e12
+    line = {
+        "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": t_ms[0].item() / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "B": B, "T": T, "H": H, "head_dim": D, "masks": MASKS,
+                   "doc_lengths": ("lognormal median 150 sigma 1.0 clip [16,4096], 5% uniform [4096,8192]" if T == 32768 else
+                                   "lognormal median 200 sigma 1.0 clip [32,2048]"),
+                   "l2": "inputs_exceed_l2 (q,k,v,dO = 1.07 GB per call)", "per_mask": per_mask,
+                   "step": "per mask: block-map pre-pass + forward + backward", "seed": SEED},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+        "gpu_launches": n_launch,
+        "clocks": clocks.result,
+        "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel<128>", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
+                     "frac": achieved / peak_tf, "peak_kind": peak_kind + " (burst)", "avg_launch_ms": bwd_ms,
+                     "algorithmic_flops_per_launch": bwd_flops, "traffic": None,
+                     "fwd": {"achieved": sum(4.0 * D * H * m["pairs"] for m in masks) / sum(p["fwd_ms"] for p in per_mask) / 1e9,
+                             "avg_launch_ms": statistics.mean(p["fwd_ms"] for p in per_mask)}},
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(steps=1)
+    print(json.dumps(line), flush=True)
+
+
+def cpu_sample():
+    """Bounded sample of the workload for the CPU arm: the first 8192 tokens of the doc_causal pack, 4 heads."""
+    from tagseq2tagseq_b200 import synth
+    from oracle import masks as om
+    pack = synth.config3_pack(SEED, "doc_causal")
+    t = 8192
+    doc = pack.doc_ids[:t]
+    dense = om.class_mask_dense(doc, None, None, None)
+    pairs = int(dense.sum())
+    g = torch.Generator().manual_seed(SEED)
+    heads = 4
+    q, k, v, do = (torch.randn(1, heads, t, D, generator=g) for _ in range(4))
+    return torch.from_numpy(dense), q, k, v, do, pairs, heads, t
+
+
+def cpu_baseline(steps: int):
+    """The oracle (fp32 dense-masked attention forward + backward, the reference's CPU path restated) on host cores."""
+    from oracle import attention as oattn
+    torch.set_num_threads(os.cpu_count() or 1)
+    dense, q, k, v, do, pairs, heads, t = cpu_sample()
+    oattn.forward_backward(q, k, v, dense, do)  # warm-up
+    times = []
+    for _ in range(max(1, steps)):
+        t0 = time.perf_counter()
+        oattn.forward_backward(q, k, v, dense, do)
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    return {"value": 14.0 * D * heads * pairs / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"doc_causal pack, first {t} tokens, {heads} heads, fp32 dense-masked attention fwd+bwd, unmasked FLOPs credited",
+            "sec_per_sample": sec}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    from oracle import attention as oattn
+    torch.set_num_threads(os.cpu_count() or 1)
+    dense, q, k, v, do, pairs, heads, t = cpu_sample()
+    for _ in range(min(args.warmup, 2)):
+        oattn.forward_backward(q, k, v, dense, do)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        oattn.forward_backward(q, k, v, dense, do)
+    sec = time.perf_counter() - t0
+    value = 14.0 * D * heads * pairs * args.steps / sec / 1e12
+    base = {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"doc_causal pack, first {t} tokens, {heads} heads per step, fp32 dense-masked attention fwd+bwd"}
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "attn_fwd_bwd_32k_mask_sweep", "B": B, "T": T, "H": H, "head_dim": D, "masks": MASKS,
+                   "note": "CPU restatement of the reference's dense-masked attention, timed on a bounded sample of the workload"},
+        "cpu_baseline": base, "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="32k", choices=["32k", "16k"],
+                    help="32k: the headline mask sweep (default).  16k: B=1, T=16384, H=16, cross_doc_link p=0.15 "
+                         "(the single-GPU 16k configuration; small enough for an ncu capture)")
+    args = ap.parse_args()
+    if args.workload == "16k":
+        global B, T, MASKS, SEED, WORKLOAD
+        B, T, MASKS, SEED, WORKLOAD = 1, 16384, ["link_p15"], 1002, "attn_fwd_bwd_16k_cross_doc_link"
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the hot path has no CPU implementation (use --impl reference for the CPU arm)")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+    try:
+        run_ours(args, rank, world, device)
+    finally:
+        if world > 1:
+            torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -94,6 +94,14 @@ int ts2ts_attn_bwd(const void* q, const void* k, const void* v, const void* out,
  * 0 = every kernel that used this plan since the last ts2ts_block_map ran to completion. */
 int ts2ts_read_status(const void* plan, void* stream, int32_t* status_out);
 
+/* Kernel timing for benchmarks.  ts2ts_profile_enable(1) makes the forward and backward calls on the
+ * current device bracket their MAIN kernel (not the small preparation / conversion launches) with CUDA
+ * events on the caller's stream; ts2ts_profile_last_ms waits for those events and returns the elapsed
+ * milliseconds of the last forward (which = 0) or backward (which = 1) main kernel in *ms (host).
+ * Has no counterpart in the reference (it times whole phases in profile_training.py:354-375). */
+int ts2ts_profile_enable(int on);
+int ts2ts_profile_last_ms(int which, float* ms);
+
 #ifdef __cplusplus
 }
 #endif

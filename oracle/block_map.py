@@ -30,6 +30,24 @@ def block_states(dense: np.ndarray, block: int = 128) -> np.ndarray:
     return st
 
 
+def block_states_streamed(doc_ids, q_row_ids, kv_col_ids, link_bits, block: int = 128) -> np.ndarray:
+    """Same map as ``block_states(class_mask_dense(...))`` computed one 128-row slab at a time, so that
+    32k-token sequences need 4 MB of mask at once instead of 1 GB."""
+    from .masks import class_mask_dense
+    t = doc_ids.shape[0]
+    nb = -(-t // block)
+    st = np.zeros((nb, nb), dtype=np.uint8)
+    for qb in range(nb):
+        q0, q1 = qb * block, min(t, (qb + 1) * block)
+        slab = class_mask_dense(doc_ids, q_row_ids, kv_col_ids, link_bits, q_range=(q0, q1))
+        pad = np.zeros((q1 - q0, nb * block), dtype=np.int32)
+        pad[:, :t] = slab
+        sums = pad.reshape(q1 - q0, nb, block).sum(axis=(0, 2))
+        st[qb, sums > 0] = PARTIAL
+        st[qb, sums == block * block] = FULL
+    return st
+
+
 def lists_from_states(state: np.ndarray):
     """Ordered lists in the BlockMask convention.  Returns a dict with
     ``kv_cnt[QB]``, ``kv_idx[QB,KB]`` (partial), ``full_cnt``, ``full_idx``,

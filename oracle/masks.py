@@ -128,8 +128,9 @@ def visualization_dense(seq_len: int, spans: Sequence, link_to_target: Dict[int,
 
 
 def class_mask_dense(doc_ids: np.ndarray, q_row_ids: Optional[np.ndarray], kv_col_ids: Optional[np.ndarray],
-                     link_bits: Optional[np.ndarray]) -> np.ndarray:
-    """bool[T,T] for the operator's own mask encoding (one batch element):
+                     link_bits: Optional[np.ndarray], q_range: Optional[Tuple[int, int]] = None) -> np.ndarray:
+    """bool[T,T] (or the row slab [q0:q1, T] when ``q_range`` is given) for the operator's own mask
+    encoding (one batch element):
 
         q >= kv and (doc[q] == doc[kv] or bit(link_bits[row[q]], col[kv]))
 
@@ -137,10 +138,11 @@ def class_mask_dense(doc_ids: np.ndarray, q_row_ids: Optional[np.ndarray], kv_co
     This is the same predicate as cross_doc_mask.py:348-357 with the grant
     test factored through (row class, column class)."""
     t = doc_ids.shape[0]
-    causal = np.arange(t)[:, None] >= np.arange(t)[None, :]
-    m = doc_ids[:, None] == doc_ids[None, :]
+    q0, q1 = (0, t) if q_range is None else q_range
+    causal = np.arange(q0, q1)[:, None] >= np.arange(t)[None, :]
+    m = doc_ids[q0:q1, None] == doc_ids[None, :]
     if link_bits is not None and link_bits.size:
-        row = doc_ids if q_row_ids is None else q_row_ids
+        row = (doc_ids if q_row_ids is None else q_row_ids)[q0:q1]
         col = doc_ids if kv_col_ids is None else kv_col_ids
         r_n, w_n = link_bits.shape
         table = np.zeros((r_n + 1, 64 * w_n + 1), dtype=bool)  # last row / col = "no class"

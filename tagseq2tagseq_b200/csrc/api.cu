@@ -7,6 +7,7 @@
 #include <stdio.h>
 
 #include "plan.h"
+#include "profile.h"
 
 namespace ts2ts {
 cudaError_t launch_block_map(PlanView P, MaskArgs M, uint8_t* state_out, int32_t* kv_cnt, int32_t* kv_idx, int32_t* full_cnt,
@@ -20,6 +21,15 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
                const int64_t* sk, const int64_t* sv, const int64_t* so, const int64_t* sdo, int B, int H, int T, int D, float scale,
                PlanView P, MaskArgs M, void* dq, void* dk, void* dv, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv,
                void* workspace, cudaStream_t stream);
+}  // namespace ts2ts
+
+namespace ts2ts {
+ProfileSlot& profile_slot() {
+  static ProfileSlot slots[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  return slots[(dev >= 0 && dev < 64) ? dev : 0];
+}
 }  // namespace ts2ts
 
 using namespace ts2ts;
@@ -166,6 +176,28 @@ int ts2ts_read_status(const void* plan, void* stream, int32_t* status_out) {
   if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(-60, "status read failed: %s", cudaGetErrorString(e));
   if (*status_out != 0) fail(*status_out, "a kernel gave up a bounded wait (code %d)", *status_out);
+  return 0;
+}
+
+int ts2ts_profile_enable(int on) {
+  ProfileSlot& s = profile_slot();
+  if (on && s.start[0] == nullptr) {
+    for (int i = 0; i < 2; ++i)
+      if (cudaEventCreate(&s.start[i]) != cudaSuccess || cudaEventCreate(&s.stop[i]) != cudaSuccess)
+        return fail(-70, "could not create timing events: %s", cudaGetErrorString(cudaGetLastError()));
+  }
+  s.enabled = on != 0;
+  s.recorded[0] = s.recorded[1] = false;
+  return 0;
+}
+
+int ts2ts_profile_last_ms(int which, float* ms) {
+  ProfileSlot& s = profile_slot();
+  if (ms == nullptr || which < 0 || which > 1) return fail(-3, "bad arguments");
+  if (!s.enabled || !s.recorded[which]) return fail(-71, "no timed launch recorded");
+  cudaError_t e = cudaEventSynchronize(s.stop[which]);
+  if (e == cudaSuccess) e = cudaEventElapsedTime(ms, s.start[which], s.stop[which]);
+  if (e != cudaSuccess) return fail(-72, "event timing failed: %s", cudaGetErrorString(e));
   return 0;
 }
 

@@ -17,6 +17,7 @@
 // (torch/_higher_order_ops/flex_attention.py:947-1075): P = exp(S - LSE), dV = P^T dO, dP = dO V^T,
 // dS = P (dP - delta), dQ = scale dS K, dK = scale dS^T Q.  Rows whose LSE is -inf get zero gradients.
 #include "plan.h"
+#include "profile.h"
 #include "ptx.cuh"
 #include "tma_host.h"
 
@@ -436,7 +437,10 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   for (int i = 0; i < 3; ++i) { p.dk_s[i] = sdk[i]; p.dv_s[i] = sdv[i]; }
   p.H = H; p.Tp = Tp; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-  attn_bwd_kernel<D><<<(unsigned)B * H * P.NB, kBwdThreads, BwdSmem<D>::kBytes, stream>>>(mq, mk, mv, mdo, mdk, mdv, p);
+  {
+    ProfileScope timed(1, stream);
+    attn_bwd_kernel<D><<<(unsigned)B * H * P.NB, kBwdThreads, BwdSmem<D>::kBytes, stream>>>(mq, mk, mv, mdo, mdk, mdv, p);
+  }
   const int64_t n8 = (int64_t)B * H * T * (D / 8);
   dq_convert_kernel<D><<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), sdq[0], sdq[1],
                                                                          sdq[2], B, H, T, Tp);

@@ -21,6 +21,7 @@
 // torch/_higher_order_ops/flex_attention.py:218-287): O = softmax(scale QK^T +
 // mask) V, LSE in natural log, a fully masked row gives O = 0 and LSE = -inf.
 #include "plan.h"
+#include "profile.h"
 #include "ptx.cuh"
 #include "tma_host.h"
 
@@ -326,7 +327,10 @@ static int launch_fwd_t(const void* q, const void* k, const void* v, void* out, 
     attr_done[dev] = true;
   }
   const unsigned grid = (unsigned)B * H * P.NB;
-  attn_fwd_kernel<D><<<grid, kFwdThreads, FwdSmem<D>::kBytes, stream>>>(mq, mk, mv, mo, p);
+  {
+    ProfileScope timed(0, stream);
+    attn_fwd_kernel<D><<<grid, kFwdThreads, FwdSmem<D>::kBytes, stream>>>(mq, mk, mv, mo, p);
+  }
   return cudaGetLastError() == cudaSuccess ? 0 : -111;
 }
 

@@ -1,0 +1,78 @@
+"""Host-side mask adapters of the package against reference-generated fixtures (CPU only)."""
+import math
+
+import numpy as np
+import pytest
+
+from oracle import masks as om
+from tagseq2tagseq_b200 import mask_spec as ms
+from tagseq2tagseq_b200 import synth
+from tests import _golden as G
+
+GRANTS = G.grant_cases()
+
+
+@pytest.mark.parametrize("entry", GRANTS, ids=[e["name"] for e in GRANTS])
+def test_grant_classes_equal_reference_bitmask_mask(entry):
+    """(row class, column class, link bits) must describe exactly the mask the reference's int64 bitmasks
+    describe -- including the grants dropped by the cap (cross_doc_mask.py:239-257)."""
+    arrs = G.grant_arrays()
+    spans, links, t = G.spans_of(entry), G.links_of(entry), entry["seq_len"]
+    cap = entry["cap"] if entry["cap"] is not None else entry["max_grants"]
+    ids = ms.build_document_ids(t, spans)
+    assert np.array_equal(ids, om.document_ids(t, spans))
+    ref = om.cross_doc_link_dense(ids, arrs[f"{entry['name']}/q_bits"], arrs[f"{entry['name']}/kv_bits"])
+    grants = ms.ordered_grants(t, spans, links, cap)
+    if grants:
+        row, col, link = ms.grant_classes(t, grants)
+        mine = om.class_mask_dense(ids, row, col, link)
+    else:
+        mine = om.doc_causal_dense(ids)
+    assert np.array_equal(mine, ref)
+
+
+def test_warmup_schedule_matches_reference_formula():
+    # cross_doc_mask.py:76-85: cosine ascent from start to max over warmup steps
+    c = ms.CrossDocLinkMaskCreator(link_detector=None, max_grants=256, max_grants_start=16, max_grants_warmup_steps=100)
+    for step in (0, 1, 37, 50, 99, 100, 500):
+        c._step = step
+        if step >= 100:
+            exp = 256
+        else:
+            exp = round(16 + (256 - 16) * (1.0 - math.cos(math.pi * step / 100)) / 2.0)
+        assert c._current_max_grants() == exp
+    assert ms.CrossDocLinkMaskCreator(None, max_grants=200)._n_chunks == 4
+    assert ms.CrossDocLinkMaskCreator(None)._current_max_grants() == 64
+
+
+def test_match_links_enforces_dag():
+    # tests/model/graph_traversal/test_cross_doc_mask.py:79-100
+    class Det:
+        def index_doc_span(self, span):
+            return span.raw_identifier
+    spans = [ms.DocSpan(0, "a", 0, 10, raw_identifier="A"), ms.DocSpan(1, "b", 10, 30, raw_identifier="B")]
+    c = ms.CrossDocLinkMaskCreator(Det())
+    links = [ms.LinkInfo(5, "B"), ms.LinkInfo(15, "A"), ms.LinkInfo(15, "missing"), ms.LinkInfo(20, "A")]
+    assert c._match_links_to_docs(links, spans) == {15: [0], 20: [0]}
+
+
+def test_registry_behaviour():
+    assert ms.list_mask_creators() == ["doc_causal"]
+    with pytest.raises(ValueError, match="Unknown mask creator"):
+        ms.get_mask_creator("sliding")
+    fn = ms.make_mask_creator_callable("doc_causal")
+    with pytest.raises(ValueError, match="tokens"):
+        fn(doc_spans=[])
+
+
+def test_synthetic_generator_is_seeded_and_counts_pairs():
+    a, b = synth.config2_pack(), synth.config2_pack()
+    assert np.array_equal(a.doc_ids, b.doc_ids) and np.array_equal(a.link_bits, b.link_bits)
+    assert a.seq_len == 16384 and a.lengths.sum() == 16384 and a.lengths.min() >= 1
+    p = synth.make_pack(5, 1500, 60, 4, 400, p_link=0.3)
+    dense = om.class_mask_dense(p.doc_ids, None, None, p.link_bits)
+    assert int(dense.sum()) == p.unmasked_pairs()
+    p1 = synth.config1_pack()
+    assert p1.seq_len == 2048 and p1.link_bits is None
+    doc, link = synth.stack_packs([synth.make_pack(1, 512, 50, 4, 100, p_link=0.5), synth.make_pack(2, 512, 20, 4, 100, p_link=0.5)])
+    assert doc.shape == (2, 512) and link.shape[0] == 2 and link.dtype == np.int64
