@@ -3,13 +3,15 @@
 // Three kernels:
 //   bwd_prep     delta[q] = sum_d O[q,d] dO[q,d],  lse2[q] = LSE[q] * log2(e)   (fp32, padded to whole tiles)
 //   attn_bwd     one CTA per 128-key tile of one (batch, head); walks the non-skipped query tiles of the
-//                transposed block list.  Per query tile, with everything transposed so that a thread owns a key row:
-//                  tcgen05  S^T = K Q^T,  dP^T = V dO^T                      (fp32 in tensor memory)
-//                  4 warps  P^T = exp2(scale S^T - lse2[q]) under the mask,  dS^T = P^T (dP^T - delta[q]);
-//                           both written as bf16 over the S^T / dP^T columns, dS^T also to shared memory
-//                  tcgen05  dV += P^T dO,  dK += dS^T Q   (A operand from tensor memory, B MN-major from smem)
-//                           dQ  = dS K                    (A = dS^T tile read MN-major, B = K MN-major)
-//                  4 warps  dQ tile -> fp32 red.global.add into the dQ accumulator
+//                transposed block list in sub-steps of 64 query rows, software-pipelined over two
+//                tensor-memory buffers so that the tensor pipe, the exponentials and the dQ reduction overlap:
+//                  tcgen05  S^T = K Q^T,  dP^T = V dO^T            [128 keys x 64 queries, fp32 in TMEM]
+//                  warps 0-3 (thread = key row)  P^T = exp2(scale S^T - lse2[q]) under the mask,
+//                           dS^T = P^T (dP^T - delta[q]); both written as bf16 over the S^T columns,
+//                           dS^T also to shared memory
+//                  tcgen05  dV += P^T dO,  dK += dS^T Q           (A from TMEM, B MN-major from smem)
+//                           dQ^T = K^T dS^T                       [D x 64 queries; A, B MN-major from smem]
+//                  warps 4-7 (thread = head-dim lane)  dQ^T -> fp32 red.global.add, 128 B per warp instruction
 //                dK (scaled) and dV leave through shared memory and TMA stores at the end.
 //   dq_convert   dQ accumulator (fp32, already scaled) -> bf16 dq
 //
@@ -38,20 +40,27 @@ struct BwdParams {
   float scale, scale_log2;
 };
 
-constexpr int kBwdThreads = 192;
+constexpr int kBwdThreads = 320;  // warps 0-3 exp/dS, 4-7 dQ reduction, 8 TMA producer, 9 MMA issuer
+constexpr int kSubQ = 64;         // query rows per pipeline sub-step
 
 template <int D>
 struct BwdSmem {
   static constexpr int kSub = D / 64;
   static constexpr int kTileBytes = kTile * D * 2;
-  static constexpr int kDsBytes = kTile * kTile * 2;
-  static constexpr int kBytes = 4 * kTileBytes + kDsBytes + 1024;
-  // tensor-memory columns
-  static constexpr int kDV = 0, kDK = D, kST = 2 * D, kDPT = 2 * D + 128;
+  static constexpr int kDsBytes = kTile * kSubQ * 2;  // one dS^T sub-step: 128 key rows x 128 B
+  // K, V, two (Q, dO) stages, two dS^T buffers, then row statistics, barriers and flags; plus alignment slack.
+  // The kernel declares no static shared memory, so the dynamic region normally starts 1024-byte aligned and the
+  // slack stays unused; if it ever does not fit, the kernel reports status 2900 instead of running.
+  static constexpr int kTiles = 6 * kTileBytes + 2 * kDsBytes;
+  static constexpr int kSmall = 4 * kTile * 4 + 16 * 8 + 16;
+  static constexpr int kSlack = 512;
+  static constexpr int kBytes = kTiles + kSmall + kSlack;
+  // tensor-memory columns: dV, dK accumulators, then two work buffers of 128 columns
+  static constexpr int kDV = 0, kDK = D, kBuf0 = 2 * D, kBuf1 = 2 * D + 128;
 };
 
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+__device__ __forceinline__ void red_add(float* addr, float v) {
+  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
 
 // 128-bit mask of the query rows of tile `qb` that may read key (doc, column class), before causality.
@@ -80,6 +89,30 @@ __device__ __forceinline__ void allowed_rows(const PlanView& P, const MaskArgs& 
   }
 }
 
+// One 32-column chunk of a sub-step: P^T and dS^T (packed bf16 pairs) from S^T, dP^T, the row statistics and the mask.
+__device__ __forceinline__ void pds_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], const float* lse2, const float* delta,
+                                          uint32_t bw, bool masked, float scale_log2, uint32_t* pk, uint32_t* dsk) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+    const float4 l4 = *reinterpret_cast<const float4*>(lse2 + e);
+    const float4 d4 = *reinterpret_cast<const float4*>(delta + e);
+    float p0 = fast_exp2(fmaf(__uint_as_float(s[e + 0]), scale_log2, -l4.x));
+    float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), scale_log2, -l4.y));
+    float p2 = fast_exp2(fmaf(__uint_as_float(s[e + 2]), scale_log2, -l4.z));
+    float p3 = fast_exp2(fmaf(__uint_as_float(s[e + 3]), scale_log2, -l4.w));
+    if (masked) {
+      p0 = ((bw >> (e + 0)) & 1u) ? p0 : 0.f;
+      p1 = ((bw >> (e + 1)) & 1u) ? p1 : 0.f;
+      p2 = ((bw >> (e + 2)) & 1u) ? p2 : 0.f;
+      p3 = ((bw >> (e + 3)) & 1u) ? p3 : 0.f;
+    }
+    pk[(e >> 1) + 0] = pack_bf16(p0, p1);
+    pk[(e >> 1) + 1] = pack_bf16(p2, p3);
+    dsk[(e >> 1) + 0] = pack_bf16(p0 * (__uint_as_float(dp[e + 0]) - d4.x), p1 * (__uint_as_float(dp[e + 1]) - d4.y));
+    dsk[(e >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dp[e + 2]) - d4.z), p3 * (__uint_as_float(dp[e + 3]) - d4.w));
+  }
+}
+
 template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
@@ -89,15 +122,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = smem;
-  uint8_t* sV = smem + Cfg::kTileBytes;
-  uint8_t* sQ = smem + 2 * Cfg::kTileBytes;
-  uint8_t* sDO = smem + 3 * Cfg::kTileBytes;
-  uint8_t* sDS = smem + 4 * Cfg::kTileBytes;
-  __shared__ uint64_t bar_kv, bar_qdo, bar_st, bar_pds, bar_g, bar_dqr, bar_epi;
-  __shared__ uint32_t tmem_slot;
-  __shared__ int abort_word;
-  __shared__ __align__(16) float s_lse2[kTile];
-  __shared__ __align__(16) float s_delta[kTile];
+  uint8_t* sV = smem + Cfg::kTileBytes;           // must follow sK directly (dQ^T operand padding for D = 64)
+  uint8_t* sQ = smem + 2 * Cfg::kTileBytes;       // two stages, Cfg::kTileBytes each
+  uint8_t* sDO = smem + 4 * Cfg::kTileBytes;      // two stages
+  uint8_t* sDS = smem + 6 * Cfg::kTileBytes;      // two buffers, Cfg::kDsBytes each
+  float (*s_lse2)[kTile] = reinterpret_cast<float (*)[kTile]>(smem + Cfg::kTiles);
+  float (*s_delta)[kTile] = reinterpret_cast<float (*)[kTile]>(smem + Cfg::kTiles + 2 * kTile * 4);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTiles + 4 * kTile * 4);
+  uint64_t& bar_kv = bars[0];
+  uint64_t* bar_qdo_full = bars + 1;
+  uint64_t* bar_qdo_free = bars + 3;
+  uint64_t* bar_st = bars + 5;
+  uint64_t* bar_pds = bars + 7;
+  uint64_t* bar_g = bars + 9;
+  uint64_t* bar_dqr = bars + 11;
+  uint64_t& bar_epi = bars[13];
+  uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 16);
+  volatile int& abort_ref = *reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars + 16) + 4);
+  volatile int* abort_ptr = &abort_ref;
+  if (smem + Cfg::kTiles + Cfg::kSmall > smem_raw + Cfg::kBytes) {  // uniform across the CTA
+    if (threadIdx.x == 0) atomicCAS(p.plan.status, 0, 2900);
+    return;
+  }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const PlanView& P = p.plan;
@@ -125,18 +171,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   }
 
   if (tid == 0) {
-    abort_word = 0;
+    *abort_ptr = 0;
     mbar_init(&bar_kv, 1);
-    mbar_init(&bar_qdo, 1);
-    mbar_init(&bar_st, 1);
-    mbar_init(&bar_pds, kTile);
-    mbar_init(&bar_g, 1);
-    mbar_init(&bar_dqr, kTile);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_qdo_full[i], 1);
+      mbar_init(&bar_qdo_free[i], 1);
+      mbar_init(&bar_st[i], 1);
+      mbar_init(&bar_pds[i], kTile);
+      mbar_init(&bar_g[i], 1);
+      mbar_init(&bar_dqr[i], kTile);
+    }
     mbar_init(&bar_epi, kTile);
     fence_mbar_init();
   }
   __syncthreads();
-  if (warp == 5) {
+  if (warp == 9) {
     tmem_alloc(&tmem_slot, 512);
     tmem_relinquish();
   }
@@ -144,12 +193,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tDV = tmem + Cfg::kDV, tDK = tmem + Cfg::kDK, tST = tmem + Cfg::kST, tDPT = tmem + Cfg::kDPT;
-  // dQ (128 q rows x D) is produced in 64-column parts into the halves of the S^T / dP^T regions that the
-  // bf16 overlays leave free.
-  const uint32_t tDQ0 = tST + 64, tDQ1 = tDPT + 64;
+  const uint32_t tDV = tmem + Cfg::kDV, tDK = tmem + Cfg::kDK;
+  // work buffer layout: S^T fp32 [0,64) and dP^T fp32 [64,128) from the tensor core; the compute warps overwrite
+  // [0,32) with P^T bf16 and [32,64) with dS^T bf16; dQ^T fp32 then lands in [64,128).
+  const uint32_t tBuf0 = tmem + Cfg::kBuf0;  // buffer bf at tBuf0 + 128 * bf
+  const int U = 2 * n;  // sub-steps
 
-  if (warp == 4) {
+  if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV); tma_prefetch_desc(&mapDO);
@@ -160,143 +210,128 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       }
       for (int i = 0; i < n; ++i) {
         const int qb = list[i] & ~kFullBit;
-        if (i > 0 && !mbar_wait(&bar_g, (i - 1) & 1, &abort_word, 11)) break;  // Q / dO of the previous tile consumed
-        mbar_expect_tx(&bar_qdo, 2 * Cfg::kTileBytes + 2 * kTile * 4);
+        const int st = i & 1;
+        if (i >= 2 && !mbar_wait(&bar_qdo_free[st], ((i - 2) >> 1) & 1, const_cast<int*>(abort_ptr), 11)) break;
+        mbar_expect_tx(&bar_qdo_full[st], 2 * Cfg::kTileBytes + 2 * kTile * 4);
         for (int s = 0; s < Cfg::kSub; ++s) {
-          tma_load_4d(sQ + s * 16384, &mapQ, &bar_qdo, s * 64, qb * kTile, h, b);
-          tma_load_4d(sDO + s * 16384, &mapDO, &bar_qdo, s * 64, qb * kTile, h, b);
+          tma_load_4d(sQ + st * Cfg::kTileBytes + s * 16384, &mapQ, &bar_qdo_full[st], s * 64, qb * kTile, h, b);
+          tma_load_4d(sDO + st * Cfg::kTileBytes + s * 16384, &mapDO, &bar_qdo_full[st], s * 64, qb * kTile, h, b);
         }
         const size_t stat = ((size_t)b * p.H + h) * p.Tp + (size_t)qb * kTile;
-        bulk_load(s_lse2, p.lse2 + stat, kTile * 4, &bar_qdo);
-        bulk_load(s_delta, p.delta + stat, kTile * 4, &bar_qdo);
+        bulk_load(s_lse2[st], p.lse2 + stat, kTile * 4, &bar_qdo_full[st]);
+        bulk_load(s_delta[st], p.delta + stat, kTile * 4, &bar_qdo_full[st]);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_st = make_idesc_bf16(128, 128, false, false);   // K-major x K-major
-      constexpr uint32_t idesc_g = make_idesc_bf16(128, D, false, true);       // TMEM A x MN-major B
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, true, true);      // MN-major A x MN-major B
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, kSubQ, false, false);  // K-major x K-major, N = 64 queries
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, D, false, true);        // TMEM A x MN-major B, N = D
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, kSubQ, true, true);    // MN-major A x MN-major B
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
-      bool ok = mbar_wait(&bar_kv, 0, &abort_word, 21);
-      for (int i = 0; i < n && ok; ++i) {
-        if (!mbar_wait(&bar_qdo, i & 1, &abort_word, 22)) break;
-        if (i > 0 && !mbar_wait(&bar_dqr, (i - 1) & 1, &abort_word, 23)) break;  // S^T / dP^T columns free again
+      bool ok = mbar_wait(&bar_kv, 0, const_cast<int*>(abort_ptr), 21);
+      // Gradient MMAs of sub-step v (reads P^T / dS^T of buffer v&1, writes dQ^T there).
+      auto grads = [&](int v) -> bool {
+        const int bf = v & 1, i = v >> 1, s = v & 1, st = i & 1;
+        if (!mbar_wait(&bar_pds[bf], (v >> 1) & 1, const_cast<int*>(abort_ptr), 24)) return false;
         tc_fence_after();
+        const uint32_t tb = (tBuf0 + 128u * bf);
+        const uint32_t qrow = (uint32_t)st * Cfg::kTileBytes + (uint32_t)s * (kSubQ * 128);  // 64 rows x 128 B into a stage
+#pragma unroll
+        for (int kk = 0; kk < kSubQ / 16; ++kk)  // dV += P^T dO   (K = 64 queries)
+          mma_ts(tDV, tb + kk * 8, make_smem_desc(aDO + qrow + kk * 2048, 16384, 1024), idesc_g, (v > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kSubQ / 16; ++kk)  // dK += dS^T Q
+          mma_ts(tDK, tb + 32 + kk * 8, make_smem_desc(aQ + qrow + kk * 2048, 16384, 1024), idesc_g, (v > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk)  // dQ^T = K^T dS^T   (K = 128 keys; M = D, padded to 128 lanes when D = 64)
+          mma_ss(tb + 64, make_smem_desc(aK + kk * 2048, 16384, 1024), make_smem_desc(aDS + bf * Cfg::kDsBytes + kk * 2048, 16384, 1024),
+                 idesc_dq, kk > 0);
+        mma_commit(&bar_g[bf]);
+        if (s == 1) mma_commit(&bar_qdo_free[st]);
+        return true;
+      };
+      for (int u = 0; u < U && ok; ++u) {
+        const int bf = u & 1, i = u >> 1, s = u & 1, st = i & 1;
+        if (s == 0 && !mbar_wait(&bar_qdo_full[st], (i >> 1) & 1, const_cast<int*>(abort_ptr), 22)) { ok = false; break; }
+        if (u >= 2 && !mbar_wait(&bar_dqr[bf], ((u - 2) >> 1) & 1, const_cast<int*>(abort_ptr), 23)) { ok = false; break; }  // buffer drained
+        tc_fence_after();
+        const uint32_t tb = (tBuf0 + 128u * bf);
+        const uint32_t qrow = (uint32_t)st * Cfg::kTileBytes + (uint32_t)s * (kSubQ * 128);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tST, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + off, 16, 1024), idesc_st, kk > 0);
+          mma_ss(tb, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + qrow + off, 16, 1024), idesc_st, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tDPT, make_smem_desc(aV + off, 16, 1024), make_smem_desc(aDO + off, 16, 1024), idesc_st, kk > 0);
+          mma_ss(tb + 64, make_smem_desc(aV + off, 16, 1024), make_smem_desc(aDO + qrow + off, 16, 1024), idesc_st, kk > 0);
         }
-        mma_commit(&bar_st);
-        if (!mbar_wait(&bar_pds, i & 1, &abort_word, 24)) break;
-        tc_fence_after();
-        const uint32_t acc = i > 0 ? 1u : 0u;
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)   // dV += P^T dO      (K = query index)
-          mma_ts(tDV, tST + kk * 8, make_smem_desc(aDO + kk * 2048, 16384, 1024), idesc_g, acc | (kk > 0));
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)   // dK += dS^T Q
-          mma_ts(tDK, tDPT + kk * 8, make_smem_desc(aQ + kk * 2048, 16384, 1024), idesc_g, acc | (kk > 0));
-#pragma unroll
-        for (int part = 0; part < Cfg::kSub; ++part) {  // dQ[:, 64 part ..] = dS K[:, 64 part ..]   (K = key index)
-          const uint32_t td = part == 0 ? tDQ0 : tDQ1;
-#pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            mma_ss(td, make_smem_desc(aDS + kk * 2048, 16384, 1024), make_smem_desc(aK + part * 16384 + kk * 2048, 16384, 1024),
-                   idesc_dq, kk > 0);
-        }
-        mma_commit(&bar_g);
+        mma_commit(&bar_st[bf]);
+        if (u >= 1 && !grads(u - 1)) { ok = false; break; }
       }
+      if (ok) grads(U - 1);
     }
-  } else {
-    // ------------------------------------------------------------------ compute warps
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ exp / dS warps, thread = key row
     const int kv = kb * kTile + tid;
     const bool kv_valid = kv < P.T;
     const int kvdoc = kv_valid ? p.mask.doc[(size_t)b * P.T + kv] : INT32_MIN;
     const int kvcol = kv_valid ? p.mask.col[(size_t)b * P.T + kv] : -1;
     const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const size_t row_base = ((size_t)b * p.H + h) * p.Tp;
     bool ok = true;
-    for (int i = 0; i < n; ++i) {
-      const int entry = list[i];
-      const int qb = entry & ~kFullBit;
-      const bool is_full = (entry & kFullBit) != 0;
-      uint32_t bits[4] = {0xffffffffu, 0xffffffffu, 0xffffffffu, 0xffffffffu};
-      if (!is_full) {
-        allowed_rows(P, p.mask, b, qb, kvdoc, kvcol, bits);
-        if (!kv_valid) bits[0] = bits[1] = bits[2] = bits[3] = 0u;
-        if (kb == qb) {  // causal inside the diagonal tile: query rows tid..127
+    uint32_t bits[4] = {0, 0, 0, 0};
+    bool masked = false;
+    for (int u = 0; u < U; ++u) {
+      const int bf = u & 1, i = u >> 1, s = u & 1, st = i & 1;
+      if (s == 0) {
+        const int entry = list[i];
+        const int qb = entry & ~kFullBit;
+        masked = (entry & kFullBit) == 0;
+        if (masked) {
+          allowed_rows(P, p.mask, b, qb, kvdoc, kvcol, bits);
+          if (!kv_valid) bits[0] = bits[1] = bits[2] = bits[3] = 0u;
+          if (kb == qb) {  // causal inside the diagonal tile: query rows tid..127
 #pragma unroll
-          for (int w = 0; w < 4; ++w) {
-            const int lo = tid - 32 * w;
-            bits[w] &= lo <= 0 ? 0xffffffffu : (lo >= 32 ? 0u : ~((1u << lo) - 1u));
+            for (int w = 0; w < 4; ++w) {
+              const int lo = tid - 32 * w;
+              bits[w] &= lo <= 0 ? 0xffffffffu : (lo >= 32 ? 0u : ~((1u << lo) - 1u));
+            }
           }
         }
+        if (!(ok = mbar_wait(&bar_qdo_full[st], (i >> 1) & 1, const_cast<int*>(abort_ptr), 30))) break;  // lse2 / delta of this tile landed
       }
-      // S^T done implies Q, dO, lse2 and delta of this tile have landed (the MMA warp waited for them)
-      if (!(ok = mbar_wait(&bar_qdo, i & 1, &abort_word, 30))) break;
-      if (!(ok = mbar_wait(&bar_st, i & 1, &abort_word, 31))) break;
+      if (!(ok = mbar_wait(&bar_st[bf], (u >> 1) & 1, const_cast<int*>(abort_ptr), 31))) break;
       tc_fence_after();
+      const uint32_t tb = (tBuf0 + 128u * bf) + lane_base;
+      uint32_t s0[32], s1[32], dp[32], pk[32], dsk[32];
+      tmem_ld32(tb, s0);
+      tmem_ld32(tb + 32, s1);
+      tmem_ld32(tb + 64, dp);
+      tmem_ld_wait();
+      const float* l2 = s_lse2[st] + s * kSubQ;
+      const float* dl = s_delta[st] + s * kSubQ;
+      pds_chunk(s0, dp, l2, dl, bits[2 * s], masked, p.scale_log2, pk, dsk);
+      tmem_ld32(tb + 96, dp);
+      tmem_ld_wait();
+      pds_chunk(s1, dp, l2 + 32, dl + 32, bits[2 * s + 1], masked, p.scale_log2, pk + 16, dsk + 16);
+      tmem_st32(tb, pk);
+      tmem_st32(tb + 32, dsk);
+      // dS^T row `tid`: 64 queries = 128 bytes = eight 16-byte chunks of this sub-step's buffer
+      uint8_t* ds_row = sDS + bf * Cfg::kDsBytes;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32], dp[32];
-        tmem_ld32(tST + lane_base + c * 32, s);
-        tmem_ld32(tDPT + lane_base + c * 32, dp);
-        tmem_ld_wait();
-        const uint32_t bw = bits[c];
-        uint32_t pk[16], dsk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          const int q0 = c * 32 + e;
-          float p0 = fast_exp2(fmaf(__uint_as_float(s[e]), p.scale_log2, -s_lse2[q0]));
-          float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), p.scale_log2, -s_lse2[q0 + 1]));
-          p0 = ((bw >> e) & 1u) ? p0 : 0.f;
-          p1 = ((bw >> (e + 1)) & 1u) ? p1 : 0.f;
-          const float d0 = p0 * (__uint_as_float(dp[e]) - s_delta[q0]);
-          const float d1 = p1 * (__uint_as_float(dp[e + 1]) - s_delta[q0 + 1]);
-          pk[e >> 1] = pack_bf16(p0, p1);
-          dsk[e >> 1] = pack_bf16(d0, d1);
-        }
-        tmem_st16(tST + lane_base + c * 16, pk);
-        tmem_st16(tDPT + lane_base + c * 16, dsk);
-        // dS^T row `tid`, query columns [32c, 32c+32): 64 bytes = four 16-byte chunks of sub-tile c/2
-#pragma unroll
-        for (int g = 0; g < 4; ++g)
-          *reinterpret_cast<uint4*>(sDS + (c >> 1) * 16384 + sw128_offset(tid, (c & 1) * 4 + g)) =
-              make_uint4(dsk[g * 4 + 0], dsk[g * 4 + 1], dsk[g * 4 + 2], dsk[g * 4 + 3]);
-      }
+      for (int g = 0; g < 8; ++g)
+        *reinterpret_cast<uint4*>(ds_row + sw128_offset(tid, g)) = make_uint4(dsk[g * 4 + 0], dsk[g * 4 + 1], dsk[g * 4 + 2], dsk[g * 4 + 3]);
       tmem_st_wait();
       fence_async_smem();
       tc_fence_before();
-      mbar_arrive(&bar_pds);
-      // ---- dQ tile: thread = query row now
-      if (!(ok = mbar_wait(&bar_g, i & 1, &abort_word, 32))) break;
-      tc_fence_after();
-      float* dst = p.dq_acc + (row_base + (size_t)qb * kTile + tid) * D;
-#pragma unroll
-      for (int part = 0; part < Cfg::kSub; ++part) {
-        const uint32_t td = part == 0 ? tDQ0 : tDQ1;
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint32_t r[32];
-          tmem_ld32(td + lane_base + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            red_add_v4(dst + part * 64 + c * 32 + e, __uint_as_float(r[e]) * p.scale, __uint_as_float(r[e + 1]) * p.scale,
-                       __uint_as_float(r[e + 2]) * p.scale, __uint_as_float(r[e + 3]) * p.scale);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(&bar_dqr);
+      mbar_arrive(&bar_pds[bf]);
     }
-    // ---- epilogue: dV, scale * dK -> bf16 -> swizzled smem (Q / dO buffers are free) -> TMA stores
+    // ---- epilogue: dV, scale * dK -> bf16 -> swizzled smem (stage 0 of Q / dO is free) -> TMA stores
+    if (ok) ok = mbar_wait(&bar_g[(U - 1) & 1], ((U - 1) >> 1) & 1, const_cast<int*>(abort_ptr), 32);
+    if (ok && U >= 2) ok = mbar_wait(&bar_g[(U - 2) & 1], ((U - 2) >> 1) & 1, const_cast<int*>(abort_ptr), 34);
+    tc_fence_after();
     if (ok) {
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
@@ -323,7 +358,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       fence_async_smem();
       mbar_arrive(&bar_epi);
     }
-    if (tid == 0 && ok && mbar_wait(&bar_epi, 0, &abort_word, 33)) {
+    if (tid == 0 && ok && mbar_wait(&bar_epi, 0, const_cast<int*>(abort_ptr), 33)) {
       for (int s = 0; s < Cfg::kSub; ++s) {
         tma_store_4d(&mapDV, sQ + s * 16384, s * 64, kb * kTile, h, b);
         tma_store_4d(&mapDK, sDO + s * 16384, s * 64, kb * kTile, h, b);
@@ -331,15 +366,39 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       tma_store_commit();
       tma_store_wait_all();
     }
+  } else {
+    // ------------------------------------------------------------------ dQ reduction warps 4-7, thread = head-dim lane
+    const int dlane = tid - kTile;  // 0..127 = TMEM lane = index into D
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const size_t row_base = ((size_t)b * p.H + h) * p.Tp;
+    for (int u = 0; u < U; ++u) {
+      const int bf = u & 1, i = u >> 1, s = u & 1;
+      const int qb = list[i] & ~kFullBit;
+      if (!mbar_wait(&bar_g[bf], (u >> 1) & 1, const_cast<int*>(abort_ptr), 41)) break;
+      tc_fence_after();
+      uint32_t r0[32], r1[32];
+      tmem_ld32((tBuf0 + 128u * bf) + lane_base + 64, r0);
+      tmem_ld32((tBuf0 + 128u * bf) + lane_base + 96, r1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&bar_dqr[bf]);  // the buffer may be overwritten while the reductions drain
+      if (dlane < D) {
+        float* dst = p.dq_acc + (row_base + (size_t)qb * kTile + s * kSubQ) * D + dlane;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) red_add(dst + (size_t)c * D, __uint_as_float(r0[c]) * p.scale);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) red_add(dst + (size_t)(32 + c) * D, __uint_as_float(r1[c]) * p.scale);
+      }
+    }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (abort_word != 0) {
-    if (tid == 0) atomicCAS(P.status, 0, 2000 + abort_word);
+  if (*abort_ptr != 0) {
+    if (tid == 0) atomicCAS(P.status, 0, 2000 + *abort_ptr);
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 5) tmem_dealloc(tmem, 512);
+  if (warp == 9) tmem_dealloc(tmem, 512);
 }
 
 // One warp per (b, h, t): delta and lse2.  Rows t >= T of the padded arrays get lse2 = +inf (P = 0) and delta = 0.
