@@ -2,17 +2,20 @@
 //
 // Three kernels:
 //   bwd_prep     delta[q] = sum_d O[q,d] dO[q,d],  lse2[q] = LSE[q] * log2(e)   (fp32, padded to whole tiles)
-//   attn_bwd     one CTA per 128-key tile of one (batch, head); walks the non-skipped query tiles of the
-//                transposed block list in sub-steps of 64 query rows, software-pipelined over two
-//                tensor-memory buffers so that the tensor pipe, the exponentials and the dQ reduction overlap:
-//                  tcgen05  S^T = K Q^T,  dP^T = V dO^T            [128 keys x 64 queries, fp32 in TMEM]
-//                  warps 0-3 (thread = key row)  P^T = exp2(scale S^T - lse2[q]) under the mask,
-//                           dS^T = P^T (dP^T - delta[q]); both written as bf16 over the S^T columns,
-//                           dS^T also to shared memory
-//                  tcgen05  dV += P^T dO,  dK += dS^T Q           (A from TMEM, B MN-major from smem)
-//                           dQ^T = K^T dS^T                       [D x 64 queries; A, B MN-major from smem]
-//                  warps 4-7 (thread = head-dim lane)  dQ^T -> fp32 red.global.add, 128 B per warp instruction
-//                dK (scaled) and dV leave through shared memory and TMA stores at the end.
+//   attn_bwd     one CTA per 128-key tile of one (batch, head); walks the non-skipped 128-query tiles of the
+//                transposed block list.  Everything is transposed so that a tensor-memory lane is a key row:
+//                  tcgen05  S^T = K Q^T,  dP^T = V dO^T            [128 keys x 128 queries, fp32 in TMEM, N = 128]
+//                  warps 0-7 (two threads per key row), in two halves of 64 queries:
+//                           P^T = exp2(scale S^T - lse2[q]) under the mask, dS^T = P^T (dP^T - delta[q]);
+//                           both written as bf16 over the S^T columns just read, dS^T also to shared memory
+//                  tcgen05  dV += P^T dO,  dK += dS^T Q           (A from TMEM, B MN-major from smem; issued per
+//                           half, so the first half's MMAs overlap the second half's exponentials)
+//                           dQ^T = K^T dS^T                       [D x 128 queries over the consumed dP^T columns]
+//                  warps 8-11 (thread = head-dim lane)  dQ^T -> scaled fp32 tile in the just-consumed Q / dO stage of
+//                           shared memory -> TMA reduce-add into the dQ accumulator, while the tensor core already
+//                           computes the next tile's S^T
+//                Q / dO tiles are double-buffered in shared memory.  dK (scaled) and dV leave through shared
+//                memory and TMA stores at the end.
 //   dq_convert   dQ accumulator (fp32, already scaled) -> bf16 dq
 //
 // Computes what the reference gets from autograd of PyTorch FlexAttention
@@ -24,6 +27,10 @@
 #include "tma_host.h"
 
 #include <math_constants.h>
+#ifdef TS2TS_TRACE
+#include <stdio.h>
+#include <stdlib.h>
+#endif
 
 namespace ts2ts {
 
@@ -38,28 +45,46 @@ struct BwdParams {
   int64_t dk_s[3], dv_s[3];
   int H, Tp;
   float scale, scale_log2;
+#ifdef TS2TS_TRACE
+  long long* trace;
+  unsigned trace_block;
+#endif
 };
 
-constexpr int kBwdThreads = 320;  // warps 0-3 exp/dS, 4-7 dQ reduction, 8 TMA producer, 9 MMA issuer
-constexpr int kSubQ = 64;         // query rows per pipeline sub-step
+#ifdef TS2TS_TRACE
+// Debug build only: per-role clock64() stamps of one CTA, written to a buffer the launcher allocates.
+#define TRACE(role, step, ev) do { if (p.trace && blockIdx.x == p.trace_block) { \
+  long long* t_ = p.trace + ((((role) * 64 + ((step) & 63)) * 8 + (ev))); *t_ = clock64(); } } while (0)
+#else
+#define TRACE(role, step, ev) do { } while (0)
+#endif
+
+constexpr int kBwdThreads = 512;  // warps 0-7 exp/dS, 8-11 dQ reduction, 12 TMA producer, 13 MMA issuer, 14-15 idle
+constexpr int kSubQ = 64;         // query columns per compute half
 
 template <int D>
 struct BwdSmem {
   static constexpr int kSub = D / 64;
   static constexpr int kTileBytes = kTile * D * 2;
-  static constexpr int kDsBytes = kTile * kSubQ * 2;  // one dS^T sub-step: 128 key rows x 128 B
-  // K, V, two (Q, dO) stages, two dS^T buffers, then row statistics, barriers and flags; plus alignment slack.
+  static constexpr int kDsBytes = kTile * kTile * 2;  // dS^T: two halves of [128 key rows x 128 B]
+  // K, V, two (Q, dO) stages, dS^T, then row statistics, barriers and flags; plus alignment slack.
   // The kernel declares no static shared memory, so the dynamic region normally starts 1024-byte aligned and the
   // slack stays unused; if it ever does not fit, the kernel reports status 2900 instead of running.
-  static constexpr int kTiles = 6 * kTileBytes + 2 * kDsBytes;
+  static constexpr int kTiles = 6 * kTileBytes + kDsBytes;
   static constexpr int kSmall = 4 * kTile * 4 + 16 * 8 + 16;
   static constexpr int kSlack = 512;
   static constexpr int kBytes = kTiles + kSmall + kSlack;
-  // tensor-memory columns: dV, dK accumulators, then two work buffers of 128 columns
-  static constexpr int kDV = 0, kDK = D, kBuf0 = 2 * D, kBuf1 = 2 * D + 128;
+  // tensor-memory columns: dV, dK accumulators, S^T (later P^T / dS^T), dP^T (later dQ^T)
+  static constexpr int kDV = 0, kDK = D, kST = 2 * D, kDPT = 2 * D + 128;
 };
 
+template <uint32_t N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <uint32_t N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+
 __device__ __forceinline__ void red_add(float* addr, float v) {
+#ifdef AB_NO_RED
+  return;
+#endif
   asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
 }
 
@@ -90,26 +115,20 @@ __device__ __forceinline__ void allowed_rows(const PlanView& P, const MaskArgs& 
 }
 
 // One 32-column chunk of a sub-step: P^T and dS^T (packed bf16 pairs) from S^T, dP^T, the row statistics and the mask.
-__device__ __forceinline__ void pds_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], const float* lse2, const float* delta,
+// One 32-column chunk of a sub-step: P^T and dS^T (packed bf16 pairs) from S^T, dP^T, the row statistics (already in
+// registers: they do not depend on the MMA results and are fetched while waiting for them) and the mask.
+__device__ __forceinline__ void pds_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], const float (&l2)[32], const float (&dl)[32],
                                           uint32_t bw, bool masked, float scale_log2, uint32_t* pk, uint32_t* dsk) {
 #pragma unroll
-  for (int e = 0; e < 32; e += 4) {
-    const float4 l4 = *reinterpret_cast<const float4*>(lse2 + e);
-    const float4 d4 = *reinterpret_cast<const float4*>(delta + e);
-    float p0 = fast_exp2(fmaf(__uint_as_float(s[e + 0]), scale_log2, -l4.x));
-    float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), scale_log2, -l4.y));
-    float p2 = fast_exp2(fmaf(__uint_as_float(s[e + 2]), scale_log2, -l4.z));
-    float p3 = fast_exp2(fmaf(__uint_as_float(s[e + 3]), scale_log2, -l4.w));
+  for (int e = 0; e < 32; e += 2) {
+    float p0 = fast_exp2(fmaf(__uint_as_float(s[e + 0]), scale_log2, -l2[e + 0]));
+    float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), scale_log2, -l2[e + 1]));
     if (masked) {
       p0 = ((bw >> (e + 0)) & 1u) ? p0 : 0.f;
       p1 = ((bw >> (e + 1)) & 1u) ? p1 : 0.f;
-      p2 = ((bw >> (e + 2)) & 1u) ? p2 : 0.f;
-      p3 = ((bw >> (e + 3)) & 1u) ? p3 : 0.f;
     }
-    pk[(e >> 1) + 0] = pack_bf16(p0, p1);
-    pk[(e >> 1) + 1] = pack_bf16(p2, p3);
-    dsk[(e >> 1) + 0] = pack_bf16(p0 * (__uint_as_float(dp[e + 0]) - d4.x), p1 * (__uint_as_float(dp[e + 1]) - d4.y));
-    dsk[(e >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dp[e + 2]) - d4.z), p3 * (__uint_as_float(dp[e + 3]) - d4.w));
+    pk[e >> 1] = pack_bf16(p0, p1);
+    dsk[e >> 1] = pack_bf16(p0 * (__uint_as_float(dp[e + 0]) - dl[e + 0]), p1 * (__uint_as_float(dp[e + 1]) - dl[e + 1]));
   }
 }
 
@@ -117,7 +136,8 @@ template <int D>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK,
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapDO,
-                const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV, const BwdParams p) {
+                const __grid_constant__ CUtensorMap mapDK, const __grid_constant__ CUtensorMap mapDV,
+                const __grid_constant__ CUtensorMap mapDQ, const BwdParams p) {
   using Cfg = BwdSmem<D>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -125,21 +145,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint8_t* sV = smem + Cfg::kTileBytes;           // must follow sK directly (dQ^T operand padding for D = 64)
   uint8_t* sQ = smem + 2 * Cfg::kTileBytes;       // two stages, Cfg::kTileBytes each
   uint8_t* sDO = smem + 4 * Cfg::kTileBytes;      // two stages
-  uint8_t* sDS = smem + 6 * Cfg::kTileBytes;      // two buffers, Cfg::kDsBytes each
+  uint8_t* sDS = smem + 6 * Cfg::kTileBytes;      // dS^T, halves of 16 KB
   float (*s_lse2)[kTile] = reinterpret_cast<float (*)[kTile]>(smem + Cfg::kTiles);
   float (*s_delta)[kTile] = reinterpret_cast<float (*)[kTile]>(smem + Cfg::kTiles + 2 * kTile * 4);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTiles + 4 * kTile * 4);
   uint64_t& bar_kv = bars[0];
-  uint64_t* bar_qdo_full = bars + 1;
-  uint64_t* bar_qdo_free = bars + 3;
-  uint64_t* bar_st = bars + 5;
-  uint64_t* bar_pds = bars + 7;
-  uint64_t* bar_g = bars + 9;
-  uint64_t* bar_dqr = bars + 11;
-  uint64_t& bar_epi = bars[13];
+  uint64_t* bar_qdo_full = bars + 1;   // [2] Q, dO, lse2, delta of a stage landed
+  uint64_t* bar_qdo_free = bars + 3;   // [2] stage reusable: its MMAs completed and the dQ tile staged in it was read by TMA
+  uint64_t& bar_st = bars[5];          // S^T and dP^T of the tile are in tensor memory
+  uint64_t* bar_pds = bars + 6;        // [2] P^T / dS^T of a 64-query half written
+  uint64_t& bar_g = bars[8];           // gradient MMAs of the tile completed (dQ^T readable)
+  uint64_t& bar_dqr = bars[9];         // dQ^T read out of tensor memory
+  uint64_t& bar_epi = bars[10];
+  uint64_t& bar_red = bars[11];        // dQ tile staged in shared memory by the reduction warps
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 16);
-  volatile int& abort_ref = *reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars + 16) + 4);
-  volatile int* abort_ptr = &abort_ref;
+  volatile int* abort_ptr = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars + 16) + 4);
+  int* abort_w = const_cast<int*>(abort_ptr);
   if (smem + Cfg::kTiles + Cfg::kSmall > smem_raw + Cfg::kBytes) {  // uniform across the CTA
     if (threadIdx.x == 0) atomicCAS(p.plan.status, 0, 2900);
     return;
@@ -176,16 +197,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_qdo_full[i], 1);
       mbar_init(&bar_qdo_free[i], 1);
-      mbar_init(&bar_st[i], 1);
-      mbar_init(&bar_pds[i], kTile);
-      mbar_init(&bar_g[i], 1);
-      mbar_init(&bar_dqr[i], kTile);
+      mbar_init(&bar_pds[i], 2 * kTile);
     }
-    mbar_init(&bar_epi, kTile);
+    mbar_init(&bar_st, 1);
+    mbar_init(&bar_g, 1);
+    mbar_init(&bar_dqr, kTile);
+    mbar_init(&bar_epi, 2 * kTile);
+    mbar_init(&bar_red, kTile);
     fence_mbar_init();
   }
   __syncthreads();
-  if (warp == 9) {
+  if (warp == 13) {
     tmem_alloc(&tmem_slot, 512);
     tmem_relinquish();
   }
@@ -193,15 +215,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tDV = tmem + Cfg::kDV, tDK = tmem + Cfg::kDK;
-  // work buffer layout: S^T fp32 [0,64) and dP^T fp32 [64,128) from the tensor core; the compute warps overwrite
-  // [0,32) with P^T bf16 and [32,64) with dS^T bf16; dQ^T fp32 then lands in [64,128).
-  const uint32_t tBuf0 = tmem + Cfg::kBuf0;  // buffer bf at tBuf0 + 128 * bf
-  const int U = 2 * n;  // sub-steps
+  const uint32_t tDV = tmem + Cfg::kDV, tDK = tmem + Cfg::kDK, tST = tmem + Cfg::kST, tDPT = tmem + Cfg::kDPT;
+  // S^T columns [64s + 32h, +32) are read by the compute thread (row, h) in half s and overwritten by it with
+  // P^T bf16 [.., +16) and dS^T bf16 [.. + 16, +16) for its 32 queries.
 
-  if (warp == 8) {
-    // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+  if (warp >= 12) {
+    reg_dec<56>();
+    if (warp == 12 && lane == 0) {
+      // ---------------------------------------------------------------- TMA producer
       tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV); tma_prefetch_desc(&mapDO);
       mbar_expect_tx(&bar_kv, 2 * Cfg::kTileBytes);
       for (int s = 0; s < Cfg::kSub; ++s) {
@@ -211,7 +232,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       for (int i = 0; i < n; ++i) {
         const int qb = list[i] & ~kFullBit;
         const int st = i & 1;
-        if (i >= 2 && !mbar_wait(&bar_qdo_free[st], ((i - 2) >> 1) & 1, const_cast<int*>(abort_ptr), 11)) break;
+        if (i >= 2 && !mbar_wait(&bar_qdo_free[st], ((i - 2) >> 1) & 1, abort_w, 11)) break;
         mbar_expect_tx(&bar_qdo_full[st], 2 * Cfg::kTileBytes + 2 * kTile * 4);
         for (int s = 0; s < Cfg::kSub; ++s) {
           tma_load_4d(sQ + st * Cfg::kTileBytes + s * 16384, &mapQ, &bar_qdo_full[st], s * 64, qb * kTile, h, b);
@@ -221,175 +242,222 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         bulk_load(s_lse2[st], p.lse2 + stat, kTile * 4, &bar_qdo_full[st]);
         bulk_load(s_delta[st], p.delta + stat, kTile * 4, &bar_qdo_full[st]);
       }
-    }
-  } else if (warp == 9) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc_st = make_idesc_bf16(128, kSubQ, false, false);  // K-major x K-major, N = 64 queries
-      constexpr uint32_t idesc_g = make_idesc_bf16(128, D, false, true);        // TMEM A x MN-major B, N = D
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, kSubQ, true, true);    // MN-major A x MN-major B
-      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
-      bool ok = mbar_wait(&bar_kv, 0, const_cast<int*>(abort_ptr), 21);
-      // Gradient MMAs of sub-step v (reads P^T / dS^T of buffer v&1, writes dQ^T there).
-      auto grads = [&](int v) -> bool {
-        const int bf = v & 1, i = v >> 1, s = v & 1, st = i & 1;
-        if (!mbar_wait(&bar_pds[bf], (v >> 1) & 1, const_cast<int*>(abort_ptr), 24)) return false;
+    } else if (warp == 13 && lane == 0) {
+      // ---------------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, 128, false, false);  // K-major x K-major
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, D, false, true);      // TMEM A x MN-major B, N = D
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, 128, true, true);    // MN-major A x MN-major B
+      // Descriptor halves (see desc_lo / desc_hi): `hi` is shared by every operand (SBO = 1024); K-major operands
+      // carry LBO 16, MN-major ones LBO 16384 (distance between the two 64-element halves of the MN extent).
+      constexpr uint32_t hi = desc_hi(1024);
+      const uint32_t k_kmaj = desc_lo(smem_u32(sK), 16), v_kmaj = desc_lo(smem_u32(sV), 16);
+      const uint32_t q_kmaj = desc_lo(smem_u32(sQ), 16), do_kmaj = desc_lo(smem_u32(sDO), 16);
+      const uint32_t q_mn = desc_lo(smem_u32(sQ), 16384), do_mn = desc_lo(smem_u32(sDO), 16384);
+      const uint32_t k_mn = desc_lo(smem_u32(sK), 16384), ds_mn = desc_lo(smem_u32(sDS), 16384);
+      bool ok = mbar_wait(&bar_kv, 0, abort_w, 21);
+      for (int i = 0; i < n && ok; ++i) {
+        const int st = i & 1;
+        const uint32_t stage = ((uint32_t)st * Cfg::kTileBytes) >> 4;
+        if (!mbar_wait(&bar_qdo_full[st], (i >> 1) & 1, abort_w, 22)) break;
+#ifdef TS2TS_STRICT_ORDER
+        if (i > 0 && !mbar_wait(&bar_g, (i - 1) & 1, abort_w, 26)) break;
+#endif
+        // S^T may be issued while dQ^T of the previous tile is still being read: it only overwrites the P^T / dS^T
+        // columns, whose readers (the dV / dK MMAs of the previous tile) were issued before the previous dQ^T MMAs.
         tc_fence_after();
-        const uint32_t tb = (tBuf0 + 128u * bf);
-        const uint32_t qrow = (uint32_t)st * Cfg::kTileBytes + (uint32_t)s * (kSubQ * 128);  // 64 rows x 128 B into a stage
+        TRACE(0, i, 0);
 #pragma unroll
-        for (int kk = 0; kk < kSubQ / 16; ++kk)  // dV += P^T dO   (K = 64 queries)
-          mma_ts(tDV, tb + kk * 8, make_smem_desc(aDO + qrow + kk * 2048, 16384, 1024), idesc_g, (v > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
+          mma_ss2(tST, k_kmaj + off, hi, q_kmaj + stage + off, hi, idesc_st, kk > 0);
+        }
+        if (i > 0 && !mbar_wait(&bar_dqr, (i - 1) & 1, abort_w, 23)) break;  // dQ^T of the previous tile read out
+        tc_fence_after();
+        TRACE(0, i, 1);
 #pragma unroll
-        for (int kk = 0; kk < kSubQ / 16; ++kk)  // dK += dS^T Q
-          mma_ts(tDK, tb + 32 + kk * 8, make_smem_desc(aQ + qrow + kk * 2048, 16384, 1024), idesc_g, (v > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
+          mma_ss2(tDPT, v_kmaj + off, hi, do_kmaj + stage + off, hi, idesc_st, kk > 0);
+        }
+        mma_commit(&bar_st);
+        TRACE(0, i, 2);
+        bool fail = false;
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          if (!mbar_wait(&bar_pds[s], i & 1, abort_w, 24)) { fail = true; break; }
+          tc_fence_after();
+          TRACE(0, i, 3 + s);
+          const uint32_t rows = stage + ((uint32_t)s * (kSubQ * 128) >> 4);  // 64 query rows x 128 B into the stage
+          const uint32_t acc = (i > 0 || s > 0) ? 1u : 0u;
+#pragma unroll
+          for (int kk = 0; kk < kSubQ / 16; ++kk)  // dV += P^T dO   (K = 64 queries of this half)
+            mma_ts2(tDV, tST + 64 * s + (kk >> 1) * 32 + (kk & 1) * 8, do_mn + rows + kk * 128, hi, idesc_g, kk > 0 ? 1u : acc);
+#pragma unroll
+          for (int kk = 0; kk < kSubQ / 16; ++kk)  // dK += dS^T Q
+            mma_ts2(tDK, tST + 64 * s + (kk >> 1) * 32 + 16 + (kk & 1) * 8, q_mn + rows + kk * 128, hi, idesc_g, kk > 0 ? 1u : acc);
+        }
+        if (fail) break;
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)  // dQ^T = K^T dS^T   (K = 128 keys; M = D, padded to 128 lanes when D = 64)
-          mma_ss(tb + 64, make_smem_desc(aK + kk * 2048, 16384, 1024), make_smem_desc(aDS + bf * Cfg::kDsBytes + kk * 2048, 16384, 1024),
-                 idesc_dq, kk > 0);
-        mma_commit(&bar_g[bf]);
-        if (s == 1) mma_commit(&bar_qdo_free[st]);
-        return true;
-      };
-      for (int u = 0; u < U && ok; ++u) {
-        const int bf = u & 1, i = u >> 1, s = u & 1, st = i & 1;
-        if (s == 0 && !mbar_wait(&bar_qdo_full[st], (i >> 1) & 1, const_cast<int*>(abort_ptr), 22)) { ok = false; break; }
-        if (u >= 2 && !mbar_wait(&bar_dqr[bf], ((u - 2) >> 1) & 1, const_cast<int*>(abort_ptr), 23)) { ok = false; break; }  // buffer drained
-        tc_fence_after();
-        const uint32_t tb = (tBuf0 + 128u * bf);
-        const uint32_t qrow = (uint32_t)st * Cfg::kTileBytes + (uint32_t)s * (kSubQ * 128);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tb, make_smem_desc(aK + off, 16, 1024), make_smem_desc(aQ + qrow + off, 16, 1024), idesc_st, kk > 0);
-        }
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tb + 64, make_smem_desc(aV + off, 16, 1024), make_smem_desc(aDO + qrow + off, 16, 1024), idesc_st, kk > 0);
-        }
-        mma_commit(&bar_st[bf]);
-        if (u >= 1 && !grads(u - 1)) { ok = false; break; }
+          mma_ss2(tDPT, k_mn + kk * 128, hi, ds_mn + kk * 128, hi, idesc_dq, kk > 0);
+        mma_commit(&bar_g);
+        TRACE(0, i, 5);
       }
-      if (ok) grads(U - 1);
     }
-  } else if (warp < 4) {
-    // ------------------------------------------------------------------ exp / dS warps, thread = key row
-    const int kv = kb * kTile + tid;
+  } else if (warp < 8) {
+    // ------------------------------------------------------------------ exp / dS warps: thread = (key row, 32 of 64 queries)
+    reg_inc<152>();
+    const int row = tid & (kTile - 1), half = tid >> 7;
+    const int kv = kb * kTile + row;
     const bool kv_valid = kv < P.T;
     const int kvdoc = kv_valid ? p.mask.doc[(size_t)b * P.T + kv] : INT32_MIN;
     const int kvcol = kv_valid ? p.mask.col[(size_t)b * P.T + kv] : -1;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
-    uint32_t bits[4] = {0, 0, 0, 0};
-    bool masked = false;
-    for (int u = 0; u < U; ++u) {
-      const int bf = u & 1, i = u >> 1, s = u & 1, st = i & 1;
-      if (s == 0) {
-        const int entry = list[i];
-        const int qb = entry & ~kFullBit;
-        masked = (entry & kFullBit) == 0;
-        if (masked) {
-          allowed_rows(P, p.mask, b, qb, kvdoc, kvcol, bits);
-          if (!kv_valid) bits[0] = bits[1] = bits[2] = bits[3] = 0u;
-          if (kb == qb) {  // causal inside the diagonal tile: query rows tid..127
+    for (int i = 0; i < n && ok; ++i) {
+      const int st = i & 1;
+      const int entry = list[i];
+      const int qb = entry & ~kFullBit;
+      const bool masked = (entry & kFullBit) == 0;
+      uint32_t bits[4] = {0, 0, 0, 0};
+      if (masked) {
+        allowed_rows(P, p.mask, b, qb, kvdoc, kvcol, bits);
+        if (!kv_valid) bits[0] = bits[1] = bits[2] = bits[3] = 0u;
+        if (kb == qb) {  // causal inside the diagonal tile: query rows row..127
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
-              const int lo = tid - 32 * w;
-              bits[w] &= lo <= 0 ? 0xffffffffu : (lo >= 32 ? 0u : ~((1u << lo) - 1u));
-            }
+          for (int w = 0; w < 4; ++w) {
+            const int lo = row - 32 * w;
+            bits[w] &= lo <= 0 ? 0xffffffffu : (lo >= 32 ? 0u : ~((1u << lo) - 1u));
           }
         }
-        if (!(ok = mbar_wait(&bar_qdo_full[st], (i >> 1) & 1, const_cast<int*>(abort_ptr), 30))) break;  // lse2 / delta of this tile landed
       }
-      if (!(ok = mbar_wait(&bar_st[bf], (u >> 1) & 1, const_cast<int*>(abort_ptr), 31))) break;
-      tc_fence_after();
-      const uint32_t tb = (tBuf0 + 128u * bf) + lane_base;
-      uint32_t s0[32], s1[32], dp[32], pk[32], dsk[32];
-      tmem_ld32(tb, s0);
-      tmem_ld32(tb + 32, s1);
-      tmem_ld32(tb + 64, dp);
-      tmem_ld_wait();
-      const float* l2 = s_lse2[st] + s * kSubQ;
-      const float* dl = s_delta[st] + s * kSubQ;
-      pds_chunk(s0, dp, l2, dl, bits[2 * s], masked, p.scale_log2, pk, dsk);
-      tmem_ld32(tb + 96, dp);
-      tmem_ld_wait();
-      pds_chunk(s1, dp, l2 + 32, dl + 32, bits[2 * s + 1], masked, p.scale_log2, pk + 16, dsk + 16);
-      tmem_st32(tb, pk);
-      tmem_st32(tb + 32, dsk);
-      // dS^T row `tid`: 64 queries = 128 bytes = eight 16-byte chunks of this sub-step's buffer
-      uint8_t* ds_row = sDS + bf * Cfg::kDsBytes;
+      if (!(ok = mbar_wait(&bar_qdo_full[st], (i >> 1) & 1, abort_w, 30))) break;  // lse2 / delta of this tile landed
 #pragma unroll
-      for (int g = 0; g < 8; ++g)
-        *reinterpret_cast<uint4*>(ds_row + sw128_offset(tid, g)) = make_uint4(dsk[g * 4 + 0], dsk[g * 4 + 1], dsk[g * 4 + 2], dsk[g * 4 + 3]);
-      tmem_st_wait();
-      fence_async_smem();
-      tc_fence_before();
-      mbar_arrive(&bar_pds[bf]);
+      for (int s = 0; s < 2; ++s) {
+        // row statistics of this thread's 32 queries: fetched before waiting for the MMAs they do not depend on
+        float l2[32], dl[32];
+        {
+          const float4* pl = reinterpret_cast<const float4*>(s_lse2[st] + s * kSubQ + 32 * half);
+          const float4* pd = reinterpret_cast<const float4*>(s_delta[st] + s * kSubQ + 32 * half);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float4 a4 = pl[e], b4 = pd[e];
+            l2[4 * e] = a4.x; l2[4 * e + 1] = a4.y; l2[4 * e + 2] = a4.z; l2[4 * e + 3] = a4.w;
+            dl[4 * e] = b4.x; dl[4 * e + 1] = b4.y; dl[4 * e + 2] = b4.z; dl[4 * e + 3] = b4.w;
+          }
+        }
+        if (s == 0 && !(ok = mbar_wait(&bar_st, i & 1, abort_w, 31))) break;
+        tc_fence_after();
+        if (tid == 0) TRACE(1, i, 4 * s + 0);
+        const uint32_t col = lane_base + 64 * s + 32 * half;
+        uint32_t sv[32], dp[32], pk[16], dsk[16];
+        tmem_ld32(tST + col, sv);
+        tmem_ld32(tDPT + col, dp);
+        tmem_ld_wait();
+        if (tid == 0) TRACE(1, i, 4 * s + 1);
+        const uint32_t bw = s == 0 ? (half == 0 ? bits[0] : bits[1]) : (half == 0 ? bits[2] : bits[3]);
+        pds_chunk(sv, dp, l2, dl, bw, masked, p.scale_log2, pk, dsk);
+        if (tid == 0) TRACE(1, i, 4 * s + 2);
+        tmem_st16(tST + col, pk);
+        tmem_st16(tST + col + 16, dsk);
+        // dS^T row `row`, queries [64 s + 32 half, +32): four 16-byte chunks of the 128-byte row of half s
+        uint8_t* ds_row = sDS + s * 16384;
+#pragma unroll
+        for (int g = 0; g < 4; ++g)
+          *reinterpret_cast<uint4*>(ds_row + sw128_offset(row, 4 * half + g)) = make_uint4(dsk[g * 4 + 0], dsk[g * 4 + 1], dsk[g * 4 + 2], dsk[g * 4 + 3]);
+        tmem_st_wait();
+        fence_async_smem();
+        tc_fence_before();
+        mbar_arrive(&bar_pds[s]);
+        if (tid == 0) TRACE(1, i, 4 * s + 3);
+      }
     }
-    // ---- epilogue: dV, scale * dK -> bf16 -> swizzled smem (stage 0 of Q / dO is free) -> TMA stores
-    if (ok) ok = mbar_wait(&bar_g[(U - 1) & 1], ((U - 1) >> 1) & 1, const_cast<int*>(abort_ptr), 32);
-    if (ok && U >= 2) ok = mbar_wait(&bar_g[(U - 2) & 1], ((U - 2) >> 1) & 1, const_cast<int*>(abort_ptr), 34);
+    // ---- epilogue: dV (query-half 0 threads) and scale * dK (half 1) -> bf16 -> swizzled smem (stage 0 of Q / dO is
+    //      free) -> TMA stores
+    //      The stage not used by the last tile is free once the dQ tile of tile n-2 has been read out of it.
+    const int est = n & 1;
+    if (ok) ok = mbar_wait(&bar_g, (n - 1) & 1, abort_w, 32);
+    if (ok && n >= 2) ok = mbar_wait(&bar_qdo_free[est], ((n - 2) >> 1) & 1, abort_w, 34);
     tc_fence_after();
     if (ok) {
+      const uint32_t tsrc = half == 0 ? tDV : tDK;
+      uint8_t* stage = (half == 0 ? sQ : sDO) + est * Cfg::kTileBytes;
+      const float f = half == 0 ? 1.f : p.scale;
 #pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const uint32_t tsrc = which == 0 ? tDV : tDK;
-        uint8_t* stage = which == 0 ? sQ : sDO;
-        const float f = which == 0 ? 1.f : p.scale;
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tsrc + lane_base + c * 32, r);
+        tmem_ld_wait();
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld32(tsrc + lane_base + c * 32, r);
-          tmem_ld_wait();
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * f, __uint_as_float(r[g * 8 + 1]) * f);
-            v.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * f, __uint_as_float(r[g * 8 + 3]) * f);
-            v.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * f, __uint_as_float(r[g * 8 + 5]) * f);
-            v.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * f, __uint_as_float(r[g * 8 + 7]) * f);
-            const int chunk = c * 4 + g;
-            *reinterpret_cast<uint4*>(stage + (chunk >> 3) * 16384 + sw128_offset(tid, chunk & 7)) = v;
-          }
+        for (int g = 0; g < 4; ++g) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(r[g * 8 + 0]) * f, __uint_as_float(r[g * 8 + 1]) * f);
+          v.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * f, __uint_as_float(r[g * 8 + 3]) * f);
+          v.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * f, __uint_as_float(r[g * 8 + 5]) * f);
+          v.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * f, __uint_as_float(r[g * 8 + 7]) * f);
+          const int chunk = c * 4 + g;
+          *reinterpret_cast<uint4*>(stage + (chunk >> 3) * 16384 + sw128_offset(row, chunk & 7)) = v;
         }
       }
       fence_async_smem();
       mbar_arrive(&bar_epi);
     }
-    if (tid == 0 && ok && mbar_wait(&bar_epi, 0, const_cast<int*>(abort_ptr), 33)) {
+    if (tid == 0 && ok && mbar_wait(&bar_epi, 0, abort_w, 33)) {
       for (int s = 0; s < Cfg::kSub; ++s) {
-        tma_store_4d(&mapDV, sQ + s * 16384, s * 64, kb * kTile, h, b);
-        tma_store_4d(&mapDK, sDO + s * 16384, s * 64, kb * kTile, h, b);
+        tma_store_4d(&mapDV, sQ + est * Cfg::kTileBytes + s * 16384, s * 64, kb * kTile, h, b);
+        tma_store_4d(&mapDK, sDO + est * Cfg::kTileBytes + s * 16384, s * 64, kb * kTile, h, b);
       }
       tma_store_commit();
       tma_store_wait_all();
     }
   } else {
-    // ------------------------------------------------------------------ dQ reduction warps 4-7, thread = head-dim lane
-    const int dlane = tid - kTile;  // 0..127 = TMEM lane = index into D
+    // ------------------------------------------------------------------ dQ reduction warps 8-11, thread = head-dim lane
+    reg_inc<152>();
+    const int dlane = tid - 2 * kTile;  // 0..127 = TMEM lane = index into D
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const size_t row_base = ((size_t)b * p.H + h) * p.Tp;
-    for (int u = 0; u < U; ++u) {
-      const int bf = u & 1, i = u >> 1, s = u & 1;
+    // shared-memory position of element (query q, this thread's d) inside the 128-byte-swizzled fp32 boxes of
+    // [128 queries x 32 floats]: box d/32 lives in the Q stage (first D/64 boxes) or the dO stage (the rest)
+    const int box = dlane >> 5, chunk = (dlane & 31) >> 2, word = dlane & 3;
+    bool ok = true;
+    for (int i = 0; i < n; ++i) {
       const int qb = list[i] & ~kFullBit;
-      if (!mbar_wait(&bar_g[bf], (u >> 1) & 1, const_cast<int*>(abort_ptr), 41)) break;
+      const int st = i & 1;
+      if (!(ok = mbar_wait(&bar_g, i & 1, abort_w, 41))) break;
       tc_fence_after();
-      uint32_t r0[32], r1[32];
-      tmem_ld32((tBuf0 + 128u * bf) + lane_base + 64, r0);
-      tmem_ld32((tBuf0 + 128u * bf) + lane_base + 96, r1);
+      if (tid == 2 * kTile) TRACE(2, i, 0);
+      uint32_t r0[32], r1[32], r2[32], r3[32];
+      tmem_ld32(tDPT + lane_base, r0);
+      tmem_ld32(tDPT + lane_base + 32, r1);
+      tmem_ld32(tDPT + lane_base + 64, r2);
+      tmem_ld32(tDPT + lane_base + 96, r3);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&bar_dqr[bf]);  // the buffer may be overwritten while the reductions drain
+      mbar_arrive(&bar_dqr);  // the dP^T / dQ^T columns may be overwritten from here on
+      if (tid == 2 * kTile) TRACE(2, i, 1);
       if (dlane < D) {
-        float* dst = p.dq_acc + (row_base + (size_t)qb * kTile + s * kSubQ) * D + dlane;
+        uint8_t* base = (box < Cfg::kSub ? sQ : sDO) + st * Cfg::kTileBytes + (box % Cfg::kSub) * 16384 + word * 4;
 #pragma unroll
-        for (int c = 0; c < 32; ++c) red_add(dst + (size_t)c * D, __uint_as_float(r0[c]) * p.scale);
-#pragma unroll
-        for (int c = 0; c < 32; ++c) red_add(dst + (size_t)(32 + c) * D, __uint_as_float(r1[c]) * p.scale);
+        for (int c = 0; c < 32; ++c) {
+          *reinterpret_cast<float*>(base + (c) * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r0[c]) * p.scale;
+          *reinterpret_cast<float*>(base + (32 + c) * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r1[c]) * p.scale;
+          *reinterpret_cast<float*>(base + (64 + c) * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r2[c]) * p.scale;
+          *reinterpret_cast<float*>(base + (96 + c) * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r3[c]) * p.scale;
+        }
+      }
+      fence_async_smem();
+      mbar_arrive(&bar_red);
+      if (tid == 2 * kTile) {
+        if (!(ok = mbar_wait(&bar_red, i & 1, abort_w, 42))) break;
+        for (int bx = 0; bx < 2 * Cfg::kSub; ++bx)
+          tma_reduce_add_4d(&mapDQ, (bx < Cfg::kSub ? sQ : sDO) + st * Cfg::kTileBytes + (bx % Cfg::kSub) * 16384, bx * 32,
+                            qb * kTile, h, b);
+        tma_store_commit();
+        tma_store_wait_read();       // shared memory read; the global reductions may still be in flight
+        mbar_arrive(&bar_qdo_free[st]);
+        TRACE(2, i, 2);
       }
     }
+    if (tid == 2 * kTile) tma_store_wait_all();
   }
 
   tc_fence_before();
@@ -398,7 +466,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     if (tid == 0) atomicCAS(P.status, 0, 2000 + *abort_ptr);
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 9) tmem_dealloc(tmem, 512);
+  if (warp == 13) tmem_dealloc(tmem, 512);
 }
 
 // One warp per (b, h, t): delta and lse2.  Rows t >= T of the padded arrays get lse2 = +inf (P = 0) and delta = 0.
@@ -470,7 +538,7 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   float* lse2 = reinterpret_cast<float*>(ws);
   float* delta = reinterpret_cast<float*>(ws + plan_align(rows * 4));
   float* dq_acc = reinterpret_cast<float*>(ws + 2 * plan_align(rows * 4));
-  CUtensorMap mq, mk, mv, mdo, mdk, mdv;
+  CUtensorMap mq, mk, mv, mdo, mdk, mdv, mdq;
   int r;
   if ((r = make_tile_map(&mq, q, 2, B, H, T, D, sq[0], sq[1], sq[2], kTile, 64))) return r;
   if ((r = make_tile_map(&mk, k, 2, B, H, T, D, sk[0], sk[1], sk[2], kTile, 64))) return r;
@@ -478,6 +546,7 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   if ((r = make_tile_map(&mdo, dout, 2, B, H, T, D, sdo[0], sdo[1], sdo[2], kTile, 64))) return r;
   if ((r = make_tile_map(&mdk, dk, 2, B, H, T, D, sdk[0], sdk[1], sdk[2], kTile, 64))) return r;
   if ((r = make_tile_map(&mdv, dv, 2, B, H, T, D, sdv[0], sdv[1], sdv[2], kTile, 64))) return r;
+  if ((r = make_tile_map(&mdq, dq_acc, 4, B, H, Tp, D, (int64_t)H * Tp * D, (int64_t)Tp * D, D, kTile, 32))) return r;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -496,13 +565,37 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   for (int i = 0; i < 3; ++i) { p.dk_s[i] = sdk[i]; p.dv_s[i] = sdv[i]; }
   p.H = H; p.Tp = Tp; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+#ifdef TS2TS_TRACE
+  static long long* trace_buf = nullptr;
+  if (!trace_buf) cudaMalloc(&trace_buf, 3 * 64 * 8 * sizeof(long long));
+  cudaMemsetAsync(trace_buf, 0, 3 * 64 * 8 * sizeof(long long), stream);
+  p.trace = trace_buf;
+  p.trace_block = getenv("TS2TS_TRACE_BLOCK") ? (unsigned)atoi(getenv("TS2TS_TRACE_BLOCK")) : 0u;
+#endif
   {
     ProfileScope timed(1, stream);
-    attn_bwd_kernel<D><<<(unsigned)B * H * P.NB, kBwdThreads, BwdSmem<D>::kBytes, stream>>>(mq, mk, mv, mdo, mdk, mdv, p);
+    attn_bwd_kernel<D><<<(unsigned)B * H * P.NB, kBwdThreads, BwdSmem<D>::kBytes, stream>>>(mq, mk, mv, mdo, mdk, mdv, mdq, p);
   }
   const int64_t n8 = (int64_t)B * H * T * (D / 8);
   dq_convert_kernel<D><<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), sdq[0], sdq[1],
                                                                          sdq[2], B, H, T, Tp);
+#ifdef TS2TS_TRACE
+  {
+    static long long host[3 * 64 * 8];
+    cudaStreamSynchronize(stream);
+    cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
+    FILE* f = fopen(getenv("TS2TS_TRACE_FILE") ? getenv("TS2TS_TRACE_FILE") : "trace.txt", "w");
+    if (f) {
+      for (int r = 0; r < 3; ++r)
+        for (int u = 0; u < 64; ++u) {
+          fprintf(f, "%d %d", r, u);
+          for (int e = 0; e < 8; ++e) fprintf(f, " %lld", host[(r * 64 + u) * 8 + e]);
+          fprintf(f, "\n");
+        }
+      fclose(f);
+    }
+  }
+#endif
   return cudaGetLastError() == cudaSuccess ? 0 : -121;
 }
 

@@ -155,7 +155,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_pv = make_idesc_bf16(128, D, false, true);
-      const uint32_t aQ = smem_u32(sQ), aK = smem_u32(sK), aV = smem_u32(sV);
+      // descriptor halves: K-major operands (Q, K) step 32 B inside a 128-byte row and 16 KB between the two
+      // 64-column halves; the MN-major operand (V) steps 16 key rows = 2048 B
+      constexpr uint32_t hi_k = desc_hi(1024);
+      const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), k_lo = desc_lo(smem_u32(sK), 16), v_lo = desc_lo(smem_u32(sV), 16384);
       bool ok = mbar_wait(&bar_q, 0, &abort_word, 21);
       for (int j = 0; j < n && ok; ++j) {
         if (!mbar_wait(&bar_k, j & 1, &abort_word, 22)) break;
@@ -163,8 +166,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk >> 2) * 16384 + (kk & 3) * 32;
-          mma_ss(tS, make_smem_desc(aQ + off, 16, 1024), make_smem_desc(aK + off, 16, 1024), idesc_s, kk > 0);
+          const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
+          mma_ss2(tS, q_lo + off, hi_k, k_lo + off, hi_k, idesc_s, kk > 0);
         }
         mma_commit(&bar_s);
         if (!mbar_wait(&bar_v, j & 1, &abort_word, 24)) break;
@@ -172,7 +175,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tc_fence_after();
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          mma_ts(tO, tS + kk * 8, make_smem_desc(aV + kk * 2048, 16384, 1024), idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+          mma_ts2(tO, tS + kk * 8, v_lo + kk * (2048 >> 4), hi_k, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         mma_commit(&bar_o);
       }
     }
