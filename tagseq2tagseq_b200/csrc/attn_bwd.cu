@@ -81,13 +81,6 @@ struct BwdSmem {
 template <uint32_t N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <uint32_t N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
-__device__ __forceinline__ void red_add(float* addr, float v) {
-#ifdef AB_NO_RED
-  return;
-#endif
-  asm volatile("red.global.add.f32 [%0], %1;" ::"l"(addr), "f"(v) : "memory");
-}
-
 // 128-bit mask of the query rows of tile `qb` that may read key (doc, column class), before causality.
 __device__ __forceinline__ void allowed_rows(const PlanView& P, const MaskArgs& M, int b, int qb, int kvdoc, int kvcol,
                                              uint32_t (&bits)[4]) {

@@ -26,6 +26,10 @@
 #include "tma_host.h"
 
 #include <math_constants.h>
+#ifdef TS2TS_TRACE
+#include <stdio.h>
+#include <stdlib.h>
+#endif
 
 namespace ts2ts {
 
@@ -37,7 +41,18 @@ struct FwdParams {
   int64_t o_sb, o_sh, o_st;
   int H;
   float scale_log2;      // softmax scale * log2(e)
+#ifdef TS2TS_TRACE
+  long long* trace;
+  unsigned trace_block;
+#endif
 };
+
+#ifdef TS2TS_TRACE
+#define FTRACE(role, step, ev) do { if (p.trace && blockIdx.x == p.trace_block) { \
+  p.trace[(((role) * 64 + ((step) & 63)) * 8 + (ev))] = clock64(); } } while (0)
+#else
+#define FTRACE(role, step, ev) do { } while (0)
+#endif
 
 constexpr int kFwdThreads = 192;
 constexpr float kRescaleThreshold = 8.0f;
@@ -162,21 +177,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       bool ok = mbar_wait(&bar_q, 0, &abort_word, 21);
       for (int j = 0; j < n && ok; ++j) {
         if (!mbar_wait(&bar_k, j & 1, &abort_word, 22)) break;
+#ifdef TS2TS_STRICT_ORDER
         if (j > 0 && !mbar_wait(&bar_o, (j - 1) & 1, &abort_word, 23)) break;  // P(j-1) consumed before S is overwritten
+#endif
+        // S(j) overwrites the columns that P(j-1) occupies; its reader, PV(j-1), was issued by this thread just
+        // before and the tensor pipe executes this thread's MMAs in issue order.
         tc_fence_after();
+        FTRACE(0, j, 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
           mma_ss2(tS, q_lo + off, hi_k, k_lo + off, hi_k, idesc_s, kk > 0);
         }
         mma_commit(&bar_s);
+        FTRACE(0, j, 1);
         if (!mbar_wait(&bar_v, j & 1, &abort_word, 24)) break;
         if (!mbar_wait(&bar_p, j & 1, &abort_word, 25)) break;
         tc_fence_after();
+        FTRACE(0, j, 2);
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
           mma_ts2(tO, tS + kk * 8, v_lo + kk * (2048 >> 4), hi_k, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
         mma_commit(&bar_o);
+        FTRACE(0, j, 3);
       }
     }
   } else {
@@ -203,20 +226,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           }
         }
       }
+      if (tid == 0) FTRACE(1, j, 0);
       if (!(ok = mbar_wait(&bar_s, j & 1, &abort_word, 31))) break;
       tc_fence_after();
-      // pass 1: row maximum of the masked, scaled scores
-      float mx = -CUDART_INF_F;
+      if (tid == 0) FTRACE(1, j, 1);
+      // pass 1: row maximum of the masked scores; eight independent running maxima keep the chain short
+      float mx8[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) mx8[i] = -CUDART_INF_F;
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
         tmem_ld32(tS + lane_base + c * 32, r);
         tmem_ld_wait();
-        const uint32_t bw = bits[c];
+        if (is_full) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if ((bw >> i) & 1u) mx = fmaxf(mx, __uint_as_float(r[i]));
+          for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(r[i]));
+        } else {
+          const uint32_t bw = bits[c];
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            mx8[i & 7] = fmaxf(mx8[i & 7], ((bw >> i) & 1u) ? __uint_as_float(r[i]) : -CUDART_INF_F);
+        }
       }
+      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      if (tid == 0) FTRACE(1, j, 2);
       mx *= p.scale_log2;  // scale > 0, so max commutes with the scaling
       const float m_new = fmaxf(m_used, mx);
       const bool need = m_new > m_used + kRescaleThreshold || (m_used == -CUDART_INF_F && m_new > -CUDART_INF_F);
@@ -236,9 +270,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         l *= factor;
         if (need) m_used = m_new;
       }
+      if (tid == 0) FTRACE(1, j, 3);
       const float m_safe = m_used == -CUDART_INF_F ? 0.f : m_used;
-      // pass 2: P = exp2(s - m), row sum, bf16 pack over the S columns
-      float sum = 0.f;
+      // pass 2: P = exp2(s - m), row sum (four independent partial sums), bf16 pack over the S columns
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         uint32_t r[32];
@@ -250,17 +285,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         for (int i = 0; i < 32; i += 2) {
           float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_safe));
           float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_safe));
-          p0 = ((bw >> i) & 1u) ? p0 : 0.f;
-          p1 = ((bw >> (i + 1)) & 1u) ? p1 : 0.f;
-          sum += p0 + p1;
+          if (!is_full) {
+            p0 = ((bw >> i) & 1u) ? p0 : 0.f;
+            p1 = ((bw >> (i + 1)) & 1u) ? p1 : 0.f;
+          }
+          sum4[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = pack_bf16(p0, p1);
         }
         tmem_st16(tS + lane_base + c * 16, pk);
       }
+      const float sum = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       l += sum;
+      if (tid == 0) FTRACE(1, j, 4);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&bar_p);
+      if (tid == 0) FTRACE(1, j, 5);
     }
     // ---- epilogue: O / l -> bf16 -> swizzled smem (Q buffer, free after the last S) -> TMA store
     if (ok) ok = mbar_wait(&bar_o, (n - 1) & 1, &abort_word, 32);
@@ -320,6 +360,13 @@ static int launch_fwd_t(const void* q, const void* k, const void* v, void* out, 
   p.plan = P; p.mask = M; p.lse = lse; p.out = static_cast<__nv_bfloat16*>(out);
   p.o_sb = so[0]; p.o_sh = so[1]; p.o_st = so[2];
   p.H = H; p.scale_log2 = scale * 1.4426950408889634f;
+#ifdef TS2TS_TRACE
+  static long long* trace_buf = nullptr;
+  if (!trace_buf) cudaMalloc(&trace_buf, 3 * 64 * 8 * sizeof(long long));
+  cudaMemsetAsync(trace_buf, 0, 3 * 64 * 8 * sizeof(long long), stream);
+  p.trace = trace_buf;
+  p.trace_block = getenv("TS2TS_TRACE_BLOCK") ? (unsigned)atoi(getenv("TS2TS_TRACE_BLOCK")) : 0u;
+#endif
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -334,6 +381,23 @@ static int launch_fwd_t(const void* q, const void* k, const void* v, void* out, 
     ProfileScope timed(0, stream);
     attn_fwd_kernel<D><<<grid, kFwdThreads, FwdSmem<D>::kBytes, stream>>>(mq, mk, mv, mo, p);
   }
+#ifdef TS2TS_TRACE
+  {
+    static long long host[3 * 64 * 8];
+    cudaStreamSynchronize(stream);
+    cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
+    FILE* f = fopen(getenv("TS2TS_FTRACE_FILE") ? getenv("TS2TS_FTRACE_FILE") : "ftrace.txt", "w");
+    if (f) {
+      for (int r = 0; r < 3; ++r)
+        for (int u = 0; u < 64; ++u) {
+          fprintf(f, "%d %d", r, u);
+          for (int e = 0; e < 8; ++e) fprintf(f, " %lld", host[(r * 64 + u) * 8 + e]);
+          fprintf(f, "\n");
+        }
+      fclose(f);
+    }
+  }
+#endif
   return cudaGetLastError() == cudaSuccess ? 0 : -111;
 }
 

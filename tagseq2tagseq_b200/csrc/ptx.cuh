@@ -233,13 +233,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-// bf16 pair by integer arithmetic (round half up on the magnitude: add 0x8000, keep the upper halves).  Differs
-// from round-to-nearest-even only on exact ties; keeps the conversion off the special-function pipe that the
-// exponentials saturate.  Inputs must be finite.
-__device__ __forceinline__ uint32_t pack_bf16_alu(float lo, float hi) {
-  const uint32_t a = __float_as_uint(lo) + 0x8000u, b = __float_as_uint(hi) + 0x8000u;
-  return __byte_perm(a, b, 0x7632);
-}
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
