@@ -253,6 +253,62 @@ def cpu_sample():
     return torch.from_numpy(dense), q, k, v, do, pairs, heads, t
 
 
+def reference_mask_and_step():
+    """The reference's own CPU code for this path, when its sources were installed under baseline/_ref
+    (pip --no-deps; they travel with the repository snapshot): dense mask from
+    CrossDocLinkMaskCreator.build_dense_mask_for_visualization (model/graph_traversal/cross_doc_mask.py:371-409),
+    attention = fp32 F.scaled_dot_product_attention + autograd (FlexAttention has no CPU backward).
+    Returns None when baseline/_ref is absent, so that the oracle port is used instead."""
+    import importlib.util
+    import types
+    from types import SimpleNamespace
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    path = os.path.join(ref, "model", "graph_traversal", "cross_doc_mask.py")
+    if not os.path.exists(path):
+        return None
+    try:
+        for name in ("model", "model.graph_traversal"):  # bare packages: model/__init__ needs tunalab, which is absent
+            if name not in sys.modules:
+                m = types.ModuleType(name)
+                m.__path__ = []
+                sys.modules[name] = m
+        mods = {}
+        for name, rel in (("model.graph_traversal.link_detector", "link_detector.py"), ("model.graph_traversal.cross_doc_mask", "cross_doc_mask.py")):
+            spec = importlib.util.spec_from_file_location(name, os.path.join(ref, "model", "graph_traversal", rel))
+            mod = importlib.util.module_from_spec(spec)
+            sys.modules[name] = mod
+            spec.loader.exec_module(mod)
+            mods[name] = mod
+        cdm = mods["model.graph_traversal.cross_doc_mask"]
+    except Exception:
+        return None
+
+    class NoLinks:
+        def detect_links(self, ids):
+            return []
+
+        def index_doc_span(self, span):
+            return span.raw_identifier
+
+    def dense_for(doc_ids):
+        spans, start = [], 0
+        t = len(doc_ids)
+        for i in range(1, t + 1):
+            if i == t or doc_ids[i] != doc_ids[start]:
+                spans.append(SimpleNamespace(doc_id=int(doc_ids[start]), start=start, end=i, raw_identifier=f"d{int(doc_ids[start])}"))
+                start = i
+        creator = cdm.CrossDocLinkMaskCreator(link_detector=NoLinks())
+        return creator.build_dense_mask_for_visualization(torch.zeros((1, t), dtype=torch.int64), spans)
+
+    def step(q, k, v, dense, do):
+        qa, ka, va = (x.clone().requires_grad_(True) for x in (q, k, v))
+        out = torch.nn.functional.scaled_dot_product_attention(qa, ka, va, attn_mask=dense)
+        out.backward(do)
+        return out
+
+    return dense_for, step
+
+
 def cpu_baseline(steps: int):
     """The oracle (fp32 dense-masked attention forward + backward, the reference's CPU path restated) on host cores."""
     from oracle import attention as oattn
@@ -276,15 +332,26 @@ def run_reference(args, rank, world):
     from oracle import attention as oattn
     torch.set_num_threads(os.cpu_count() or 1)
     dense, q, k, v, do, pairs, heads, t = cpu_sample()
+    ref = reference_mask_and_step()
+    kind = "port"
+    run = lambda: oattn.forward_backward(q, k, v, dense, do)
+    if ref is not None:
+        from tagseq2tagseq_b200 import synth
+        dense_for, step = ref
+        ref_dense = dense_for(synth.config3_pack(SEED, "doc_causal").doc_ids[:t])
+        if torch.equal(ref_dense, dense):  # the reference's own mask construction agrees with the port's
+            kind = "reference"
+            run = lambda: step(q, k, v, ref_dense, do)
     for _ in range(min(args.warmup, 2)):
-        oattn.forward_backward(q, k, v, dense, do)
+        run()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        oattn.forward_backward(q, k, v, dense, do)
+        run()
     sec = time.perf_counter() - t0
     value = 14.0 * D * heads * pairs * args.steps / sec / 1e12
-    base = {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"doc_causal pack, first {t} tokens, {heads} heads per step, fp32 dense-masked attention fwd+bwd"}
+    base = {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"doc_causal pack, first {t} tokens, {heads} heads per step, fp32 dense-masked attention fwd+bwd"
+                      + (" (reference mask code from baseline/_ref + torch SDPA autograd)" if kind == "reference" else " (oracle port)")}
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
