@@ -90,6 +90,32 @@ int ts2ts_attn_bwd(const void* q, const void* k, const void* v, const void* out,
                    void* dv, const int64_t* dq_strides, const int64_t* dk_strides, const int64_t* dv_strides,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* Backward without any caller-provided or freshly allocated scratch.  It has no counterpart in the reference.
+ *
+ * Who needs it: hosts that cannot obtain device memory at the moment of the call -- a process whose whole HBM
+ * was handed to another allocator at start-up, a plug-in that may not call cudaMalloc because that call
+ * synchronises the device and would stall unrelated streams, or a C caller with no allocator of its own.
+ * For them the scratch of ts2ts_attn_bwd (fp32 dQ accumulator, delta, scaled LSE) lives in one array compiled
+ * into the library; every GPU that loads the library keeps that array until the process ends.
+ *
+ * Same arguments and results as ts2ts_attn_bwd, minus the workspace.  Limits and rules:
+ *   - the problem must satisfy ts2ts_attn_bwd_workspace_bytes(B,H,T,D) <= ts2ts_attn_bwd_noalloc_max_bytes()
+ *     (64 MiB, e.g. H * ceil(T/128)*128 <= 129055 rows at D = 128); larger problems are rejected with -10;
+ *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *     current) and caches it, so make the first call on each device before starting any stream capture;
+ *   - the call allocates nothing: no cudaMalloc / cudaFree and no allocating library routine;
+ *   - all calls on a device share the one array, which still holds the previous call's values: each call
+ *     re-zeroes the accumulator part and rewrites the rest before use, and two calls whose kernels can
+ *     overlap on the GPU (different streams without ordering) race -- serialise them. */
+size_t ts2ts_attn_bwd_noalloc_max_bytes(void);
+int ts2ts_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                           const float* lse, const int64_t* q_strides, const int64_t* k_strides,
+                           const int64_t* v_strides, const int64_t* out_strides, const int64_t* dout_strides, int B,
+                           int H, int T, int D, float scale, const int32_t* doc_ids, const int32_t* q_row_ids,
+                           const int32_t* kv_col_ids, const int64_t* link_bits, int R, int W, const void* plan,
+                           size_t plan_bytes, void* dq, void* dk, void* dv, const int64_t* dq_strides,
+                           const int64_t* dk_strides, const int64_t* dv_strides, void* stream);
+
 /* Waits for `stream`, then copies the plan's device status word to *status_out (host).
  * 0 = every kernel that used this plan since the last ts2ts_block_map ran to completion. */
 int ts2ts_read_status(const void* plan, void* stream, int32_t* status_out);

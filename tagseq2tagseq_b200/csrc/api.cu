@@ -21,6 +21,7 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
                const int64_t* sk, const int64_t* sv, const int64_t* so, const int64_t* sdo, int B, int H, int T, int D, float scale,
                PlanView P, MaskArgs M, void* dq, void* dk, void* dv, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv,
                void* workspace, cudaStream_t stream);
+int bwd_static_scratch(void** ptr, size_t* bytes);
 }  // namespace ts2ts
 
 namespace ts2ts {
@@ -168,6 +169,33 @@ int ts2ts_attn_bwd(const void* q, const void* k, const void* v, const void* out,
                  workspace, static_cast<cudaStream_t>(stream));
   if (r) return fail(r, "backward launch failed (code %d, CUDA: %s)", r, cudaGetErrorString(cudaPeekAtLastError()));
   return 0;
+}
+
+size_t ts2ts_attn_bwd_noalloc_max_bytes(void) {
+  void* ptr = nullptr;
+  size_t bytes = 0;
+  return bwd_static_scratch(&ptr, &bytes) == 0 ? bytes : 0;
+}
+
+int ts2ts_attn_bwd_noalloc(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse,
+                           const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                           const int64_t* out_strides, const int64_t* dout_strides, int B, int H, int T, int D, float scale,
+                           const int32_t* doc_ids, const int32_t* q_row_ids, const int32_t* kv_col_ids, const int64_t* link_bits,
+                           int R, int W, const void* plan, size_t plan_bytes, void* dq, void* dk, void* dv,
+                           const int64_t* dq_strides, const int64_t* dk_strides, const int64_t* dv_strides, void* stream) {
+  int r;
+  if ((r = check_shape(B, H, T, D))) return r;
+  void* scratch = nullptr;
+  size_t scratch_bytes = 0;
+  if ((r = bwd_static_scratch(&scratch, &scratch_bytes)))
+    return fail(r, "could not resolve the built-in scratch array on this device: %s", cudaGetErrorString(cudaPeekAtLastError()));
+  const size_t need = bwd_workspace_bytes(B, H, T, D);
+  if (need > scratch_bytes)
+    return fail(-10, "this problem needs %zu bytes of scratch but the built-in array holds %zu; use ts2ts_attn_bwd with a "
+                     "caller-owned workspace", need, scratch_bytes);
+  return ts2ts_attn_bwd(q, k, v, out, dout, lse, q_strides, k_strides, v_strides, out_strides, dout_strides, B, H, T, D, scale,
+                        doc_ids, q_row_ids, kv_col_ids, link_bits, R, W, plan, plan_bytes, dq, dk, dv, dq_strides, dk_strides,
+                        dv_strides, scratch, scratch_bytes, stream);
 }
 
 int ts2ts_read_status(const void* plan, void* stream, int32_t* status_out) {

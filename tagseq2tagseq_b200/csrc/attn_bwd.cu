@@ -603,4 +603,27 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
   return -122;
 }
 
+// --------------------------------------------------------------------------------------------------------------
+// Scratch that lives inside the library, for ts2ts_attn_bwd_noalloc (see include/ts2ts_attn.h).
+//
+// `g_static_scratch` is a device array.  Host code must not use the name as a pointer: on the host it is only a
+// handle, and a kernel handed that handle would read or write unrelated memory.  The device address is asked for
+// once per device with cudaGetSymbolAddress, with that device current, and cached.
+constexpr size_t kStaticScratchBytes = size_t(64) << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int bwd_static_scratch(void** ptr, size_t* bytes) {
+  static void* cached[64] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -130;
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_scratch) != cudaSuccess || p == nullptr) return -131;
+    cached[dev] = p;
+  }
+  *ptr = cached[dev];
+  *bytes = kStaticScratchBytes;
+  return 0;
+}
+
 }  // namespace ts2ts
