@@ -206,6 +206,12 @@ def run_ours(args, rank, world, device):
     h2d = 4 * tens * len(masks) + mask_bytes
     d2h = (4 * tens + B * H * T * 4) * len(masks)
 
+    train = None
+    if WORKLOAD == "attn_fwd_bwd_32k_mask_sweep" and not args.no_train:
+        del hq, hk, hv, hdo, h_out, h_dq, h_dk, h_dv, dq_, dk_, dv_, do_, q, k, v, do
+        torch.cuda.empty_cache()
+        train = run_train(args, rank, world, device, "train4", steps=max(2, min(args.steps, 5)), warmup=3)
+
     t_ms = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
     fl = torch.tensor([total_flops, sum(flops_of(m["pairs"]) for m in masks) * e2e_steps], device=device, dtype=torch.float64)
     if world > 1:
@@ -235,7 +241,55 @@ def run_ours(args, rank, world, device):
     }
     if world == 1:
         line["cpu_baseline"] = cpu_baseline(steps=1)
-    print(json.dumps(line), flush=True)
+    if train is not None:
+        line["train_step"] = train
+    emit(line)
+
+
+def run_train(args, rank, world, device, which: str, steps: int, warmup: int):
+    """Training step of the 12-layer (train4) or 24-layer (train5) decoder LM, one packed sequence per rank, DDP."""
+    from tagseq2tagseq_b200 import synth
+    from tagseq2tagseq_b200.mask_spec import MaskSpec
+    from tagseq2tagseq_b200.replicas import aggregate, rank_seed
+    from tagseq2tagseq_b200.train_step import TrainStep, config4, config5, train_flops_per_step
+    cfg, t_len, base = (config4(), 16384, 1004) if which == "train4" else (config5(), 32768, 1005)
+    ts = TrainStep(cfg, device, world)
+    n_packs = 4  # a small rotation of packs per rank, all resident on the device
+    packs = [synth.config2_pack(rank_seed(base, rank, i)) if which == "train4" else synth.config5_pack(rank_seed(base, rank, i))
+             for i in range(n_packs)]
+    g = torch.Generator().manual_seed(rank_seed(base, rank))
+    batches = []
+    for pk in packs:
+        doc_np, link_np = synth.stack_packs([pk])
+        spec = MaskSpec(doc_ids=torch.from_numpy(doc_np).to(device), link_bits=torch.from_numpy(link_np).to(device))
+        tokens = torch.randint(0, cfg.vocab, (1, t_len + 1), generator=g).to(device)
+        batches.append((tokens, spec, pk.unmasked_pairs()))
+    for i in range(warmup):
+        tok, spec, _ = batches[i % n_packs]
+        spec._block_map = None
+        loss = ts.step(tok, spec)
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize(device)
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    flops = 0.0
+    for i in range(steps):
+        tok, spec, pairs = batches[i % n_packs]
+        spec._block_map = None  # the pre-pass is part of every step, as in the reference (one mask build per micro-batch)
+        loss = ts.step(tok, spec)
+        flops += train_flops_per_step(cfg, t_len, pairs)
+    ev1.record()
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize(device)
+    (ms,), (tot_flops, tot_tokens) = aggregate([ev0.elapsed_time(ev1)], [flops, float(t_len * steps)], device)
+    peak_tf, _, kind = measured_peaks()
+    return {"metric": "train tokens/s", "value": tot_tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms / steps, "steps": steps,
+            "model": f"{cfg.n_layers}L d{cfg.d_model} {cfg.n_heads}h hd{cfg.head_dim} swiglu{cfg.mlp_hidden} V{cfg.vocab}",
+            "seq_len": t_len, "global_batch_tokens": t_len * world, "parallelism": f"ddp{world}", "optimizer": "fused AdamW (fp32 params, bf16 autocast)",
+            "model_tflops": tot_flops / (ms * 1e-3) / 1e12, "frac_of_peak": tot_flops / (ms * 1e-3) / 1e12 / (peak_tf * world),
+            "peak_kind": kind, "loss": float(loss)}
 
 
 def cpu_sample():
@@ -352,23 +406,38 @@ def run_reference(args, rank, world):
     base = {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": kind,
             "sample": f"doc_causal pack, first {t} tokens, {heads} heads per step, fp32 dense-masked attention fwd+bwd"
                       + (" (reference mask code from baseline/_ref + torch SDPA autograd)" if kind == "reference" else " (oracle port)")}
-    print(json.dumps({
+    emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": sec / args.steps * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": "attn_fwd_bwd_32k_mask_sweep", "B": B, "T": T, "H": H, "head_dim": D, "masks": MASKS,
                    "note": "CPU restatement of the reference's dense-masked attention, timed on a bounded sample of the workload"},
         "cpu_baseline": base, "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0}), flush=True)
+        "gpu_launches": 0})
+
+
+_REAL_STDOUT = None
+
+
+def emit(obj) -> None:
+    """The one JSON line goes to the process's original stdout; everything else (NCCL banners, warnings) was
+    redirected to stderr in main()."""
+    out = _REAL_STDOUT or sys.stdout
+    out.write(json.dumps(obj) + "\n")
+    out.flush()
 
 
 def main():
+    global _REAL_STDOUT
+    _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)  # libraries that print to fd 1 (e.g. the NCCL version banner) must not pollute the JSON line
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="32k", choices=["32k", "16k"],
+    ap.add_argument("--no-train", action="store_true", help="skip the short training-step measurement appended to the 32k line")
+    ap.add_argument("--workload", default="32k", choices=["32k", "16k", "train4", "train5"],
                     help="32k: the headline mask sweep (default).  16k: B=1, T=16384, H=16, cross_doc_link p=0.15 "
                          "(the single-GPU 16k configuration; small enough for an ncu capture)")
     args = ap.parse_args()
@@ -389,7 +458,14 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=device)
     try:
-        run_ours(args, rank, world, device)
+        if args.workload in ("train4", "train5"):
+            res = run_train(args, rank, world, device, args.workload, steps=args.steps, warmup=max(3, args.warmup))
+            if rank == 0:
+                res.update({"n_gpus": world, "warmup": max(3, args.warmup), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                            "dtype": "bf16", "data": "synthetic", "config": {"workload": args.workload}})
+                emit(res)
+        else:
+            run_ours(args, rank, world, device)
     finally:
         if world > 1:
             torch.distributed.destroy_process_group()

@@ -66,7 +66,7 @@ __device__ __forceinline__ void fence_async_smem() {  // generic-proxy smem writ
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 
-// ----------------------------------------------------------------------------- TMA (no multicast anywhere)
+// ----------------------------------------------------------------------------- TMA (every copy targets this CTA only)
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
 }

@@ -1,0 +1,140 @@
+"""Decoder-only LM training step around the masked-attention operator, with DDP over NCCL.
+
+This is the scaling half of the benchmark: the call order of the reference's training module
+(model/modules/training_module.py:195-211: shift tokens, build the mask once, embed -> backbone -> norm -> logits ->
+cross-entropy) and its DDP settings (main.py:404-415: static graph, no unused parameters, 256 MB buckets), with a
+plain pre-norm decoder (RMSNorm, fused QKV, RoPE, SwiGLU) standing in for the reference's tunalab modules, which are
+not available.  The attention call inside every layer is `ts2ts::masked_attn`; the block plan is built once per
+micro-batch and shared by all layers, as the reference shares its BlockMask (block_mask_creator.py:132-139).
+Everything except the attention operator is ordinary PyTorch (cuBLAS GEMMs, fused AdamW): plumbing, not the product.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .attention import masked_attn
+from .mask_spec import MaskSpec
+
+
+@dataclass
+class LMConfig:
+    n_layers: int = 12
+    d_model: int = 768
+    n_heads: int = 12
+    head_dim: int = 64
+    mlp_hidden: int = 3072
+    vocab: int = 50304
+    rope_base: float = 10000.0
+
+    @property
+    def matmul_params(self) -> int:
+        """Parameters that take part in a GEMM per token (all linear layers and the output head)."""
+        d, hd = self.d_model, self.n_heads * self.head_dim
+        per_layer = d * 3 * hd + hd * d + 3 * d * self.mlp_hidden
+        return self.n_layers * per_layer + d * self.vocab
+
+
+def config4() -> LMConfig:
+    return LMConfig(12, 768, 12, 64, 3072, 50304)
+
+
+def config5() -> LMConfig:
+    # SwiGLU hidden int(8/3 * 2048) = 5461 (model/modules/layer.py:26) rounded up to a multiple of 128 for GEMM alignment
+    return LMConfig(24, 2048, 16, 128, 5504, 50304)
+
+
+def rope_tables(T: int, head_dim: int, base: float, device, dtype=torch.float32):
+    inv = 1.0 / (base ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
+    ang = torch.arange(T, device=device, dtype=torch.float32)[:, None] * inv[None, :]
+    return ang.cos().to(dtype), ang.sin().to(dtype)
+
+
+def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """x [B,H,T,D]; rotate pairs (first half, second half)."""
+    h = x.shape[-1] // 2
+    x1, x2 = x[..., :h], x[..., h:]
+    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+
+
+class Block(nn.Module):
+    def __init__(self, cfg: LMConfig):
+        super().__init__()
+        hd = cfg.n_heads * cfg.head_dim
+        self.cfg = cfg
+        self.ln1 = nn.RMSNorm(cfg.d_model)
+        self.qkv = nn.Linear(cfg.d_model, 3 * hd, bias=False)
+        self.proj = nn.Linear(hd, cfg.d_model, bias=False)
+        self.ln2 = nn.RMSNorm(cfg.d_model)
+        self.gate_up = nn.Linear(cfg.d_model, 2 * cfg.mlp_hidden, bias=False)
+        self.down = nn.Linear(cfg.mlp_hidden, cfg.d_model, bias=False)
+
+    def forward(self, x, mask: MaskSpec, cos, sin):
+        B, T, _ = x.shape
+        c = self.cfg
+        qkv = self.qkv(self.ln1(x)).view(B, T, 3, c.n_heads, c.head_dim)
+        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))          # [B,H,T,D] strided views
+        q, k = apply_rope(q, cos, sin).to(v.dtype), apply_rope(k, cos, sin).to(v.dtype)
+        out, _ = masked_attn(q, k, v, mask.doc_ids, mask.link_bits, q_row_ids=mask.q_row_ids, kv_col_ids=mask.kv_col_ids,
+                             plan=mask.plan)                                      # x + attn(ln(x)), layer.py:32-35
+        x = x + self.proj(out.transpose(1, 2).reshape(B, T, c.n_heads * c.head_dim))
+        g, u = self.gate_up(self.ln2(x)).chunk(2, dim=-1)
+        return x + self.down(F.silu(g) * u)
+
+
+class DecoderLM(nn.Module):
+    def __init__(self, cfg: LMConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.embed = nn.Embedding(cfg.vocab, cfg.d_model)
+        self.blocks = nn.ModuleList(Block(cfg) for _ in range(cfg.n_layers))
+        self.norm = nn.RMSNorm(cfg.d_model)
+        self.head = nn.Linear(cfg.d_model, cfg.vocab, bias=False)
+        for p in self.parameters():
+            if p.dim() >= 2:
+                nn.init.normal_(p, std=0.02)
+
+    def forward(self, tokens: torch.Tensor, mask: MaskSpec) -> torch.Tensor:
+        """tokens int64 [B, T+1]; returns the mean next-token cross-entropy (training_module.py:195-211)."""
+        inp, tgt = tokens[:, :-1], tokens[:, 1:]
+        T = inp.shape[1]
+        cos, sin = rope_tables(T, self.cfg.head_dim, self.cfg.rope_base, inp.device)
+        x = self.embed(inp)
+        for blk in self.blocks:
+            x = blk(x, mask, cos, sin)
+        logits = self.head(self.norm(x))
+        return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), tgt.reshape(-1))
+
+
+class TrainStep:
+    """One optimizer step on one packed sequence per rank: forward under bf16 autocast, backward (DDP all-reduces
+    the gradients over NCCL in 256 MB buckets, overlapped with the backward), fused AdamW."""
+
+    def __init__(self, cfg: LMConfig, device: torch.device, world: int = 1, lr: float = 3e-4, seed: int = 0):
+        torch.manual_seed(seed)  # identical initial weights on every rank
+        self.cfg, self.device, self.world = cfg, device, world
+        model = DecoderLM(cfg).to(device)
+        self.model = model
+        if world > 1:
+            self.model = torch.nn.parallel.DistributedDataParallel(
+                model, device_ids=[device.index], static_graph=True, find_unused_parameters=False, bucket_cap_mb=256,
+                gradient_as_bucket_view=True)
+        self.opt = torch.optim.AdamW(model.parameters(), lr=lr, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
+
+    def step(self, tokens: torch.Tensor, mask: MaskSpec) -> torch.Tensor:
+        self.opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = self.model(tokens, mask)
+        loss.backward()
+        self.opt.step()
+        return loss.detach()
+
+
+def train_flops_per_step(cfg: LMConfig, T: int, unmasked_pairs: int) -> float:
+    """6 * P_matmul * T for the linear layers (forward + backward) plus 14 * D * H * N per layer for attention."""
+    return 6.0 * cfg.matmul_params * T + cfg.n_layers * 14.0 * cfg.head_dim * cfg.n_heads * unmasked_pairs

@@ -1,0 +1,54 @@
+"""Multi-rank host logic on CPU: two gloo ranks own different packs and their measurements combine as max / sum."""
+import os
+import socket
+
+import numpy as np
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from tagseq2tagseq_b200 import synth
+        from tagseq2tagseq_b200.replicas import aggregate, rank_seed
+        pack = synth.make_pack(rank_seed(1003, rank), 4096, 150, 16, 1024, p_link=0.1)
+        pairs = pack.unmasked_pairs()
+        ms, work = aggregate([10.0 + 5.0 * rank, 1.0], [float(pairs), 1.0])
+        gathered = [None] * world
+        dist.all_gather_object(gathered, (int(pack.doc_ids.sum()), pairs))
+        if rank == 0:
+            out.put((ms, work, gathered))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_ranks_own_different_packs_and_aggregate():
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    ms, work, gathered = out.get(timeout=120)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert ms == [15.0, 1.0]                      # max over ranks
+    assert gathered[0] != gathered[1]             # per-rank seeds give different packs
+    assert work == [float(gathered[0][1] + gathered[1][1]), 2.0]   # sum over ranks
+
+
+def test_aggregate_without_process_group_is_identity():
+    from tagseq2tagseq_b200.replicas import aggregate, rank_seed
+    assert aggregate([3.0], [7.0]) == ([3.0], [7.0])
+    assert rank_seed(1003, 2, 1) == 3004
