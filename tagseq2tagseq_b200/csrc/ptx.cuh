@@ -238,19 +238,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x on the FMA / integer pipes (no special-function unit): round x to the nearest integer n with the
-// 1.5 * 2^23 trick, evaluate a cubic for 2^(x - n) on [-0.5, 0.5] (relative error 8e-5, far below bf16
-// resolution) and add n to the exponent field.  Used for a fraction of the exponentials so that the 16-per-clock
-// special-function unit is not the only pipe they occupy.  x is clamped to >= -126 (result >= 2^-126).
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -126.f);
-  const float t = x + 12582912.f;
-  const float r = x - (t - 12582912.f);
-  float y = fmaf(0.05508868396282196f, r, 0.24260404706001282f);
-  y = fmaf(y, r, 0.6932762265205383f);
-  y = fmaf(y, r, 0.9999289512634277f);
-  return __int_as_float(__float_as_int(y) + (__float_as_int(t) << 23));
-}
 // Byte offset of 16-byte chunk `chunk` (0..7) of row `row` inside a [rows x 128 B] tile
 // written with the 128-byte swizzle (the layout TMA SWIZZLE_128B produces and that the
 // K-major / MN-major 128B-swizzle descriptors above read).  The tile base is 1024-B aligned.
