@@ -446,6 +446,76 @@ def run_reference(args, rank, world):
         "gpu_launches": 0})
 
 
+def run_flex_gpu(args, rank, world, device):
+    """The reference's GPU attention path on the same inputs, for comparison: torch.compile(flex_attention)
+    (Inductor's Triton templates, reached from model/modules/layer.py:33) with a BlockMask from create_block_mask and
+    a mask_mod equal to the reference's (cross_doc_mask.py:348-357) expressed over (doc ids, link bits).
+    Library code only; none of this package's kernels run in this mode."""
+    from torch.nn.attention.flex_attention import create_block_mask, flex_attention
+    masks = make_workload(rank, device)
+    torch.manual_seed(SEED + rank)
+    q, k, v, do = (torch.randn(B, H, T, D, device=device, dtype=torch.float32).bfloat16() for _ in range(4))
+    q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
+    compiled = torch.compile(flex_attention, dynamic=False)
+    # The stock template configuration can exceed the 227 KB of shared memory at head_dim 128; smaller tiles are tried
+    # in turn and the options that worked are reported.
+    option_sets = [None, {"num_stages": 2}, {"BLOCK_M": 64, "BLOCK_N": 64, "BLOCK_M1": 32, "BLOCK_N1": 64, "BLOCK_M2": 64, "BLOCK_N2": 32},
+                   {"BLOCK_M": 64, "BLOCK_N": 32, "BLOCK_M1": 32, "BLOCK_N1": 32, "BLOCK_M2": 32, "BLOCK_N2": 32, "num_stages": 1}]
+    used_options = "unset"
+    per_mask, tot_ms, tot_flops = [], 0.0, 0.0
+    for m in masks:
+        doc, link = m["doc"], m["link"]
+        if link is None:
+            def mask_mod(b, h, qi, ki, doc=doc):
+                return (qi >= ki) & (doc[b, qi] == doc[b, ki])
+        else:
+            def mask_mod(b, h, qi, ki, doc=doc, link=link):
+                dq_, dk_ = doc[b, qi], doc[b, ki]
+                word = link[b, dq_, dk_ >> 6]
+                return (qi >= ki) & ((dq_ == dk_) | (((word >> (dk_ & 63)) & 1) != 0))
+        t0 = time.perf_counter()
+        bm = create_block_mask(mask_mod, B, None, T, T, device=device, _compile=True)
+        torch.cuda.synchronize(device)
+        mask_s = time.perf_counter() - t0
+        used_options = "unset"  # searched per mask: a mask_mod that captures more tensors needs more resources
+        if used_options == "unset":
+            errors = []
+            for opts in option_sets:
+                try:
+                    torch._dynamo.reset()
+                    out = compiled(q, k, v, block_mask=bm, kernel_options=opts)
+                    out.backward(do)
+                    torch.cuda.synchronize(device)
+                    used_options = opts
+                    break
+                except Exception as exc:  # noqa: BLE001 - report and try the next configuration
+                    errors.append(f"{opts}: {str(exc).splitlines()[0][:160]}")
+            if used_options == "unset":
+                emit({"impl": "flex_gpu", "unavailable": "no FlexAttention template configuration compiled: " + " | ".join(errors)})
+                return
+        for _ in range(3):
+            out = compiled(q, k, v, block_mask=bm, kernel_options=used_options)
+            out.backward(do)
+        torch.cuda.synchronize(device)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            out = compiled(q, k, v, block_mask=bm, kernel_options=used_options)
+            out.backward(do)
+        ev1.record()
+        torch.cuda.synchronize(device)
+        ms = ev0.elapsed_time(ev1) / args.steps
+        per_mask.append({"mask": m["name"], "fwd_bwd_ms": ms, "tflops": flops_of(m["pairs"]) / ms / 1e9, "first_block_mask_s": mask_s,
+                         "kernel_options": used_options})
+        tot_ms += ms
+        tot_flops += flops_of(m["pairs"])
+    emit({"impl": "flex_gpu", "metric": METRIC, "value": tot_flops / tot_ms / 1e9, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+          "ms_per_step": tot_ms, "dtype": "bf16", "data": "synthetic", "higher_is_better": True,
+          "config": {"workload": WORKLOAD, "B": B, "T": T, "H": H, "head_dim": D, "per_mask": per_mask,
+                     "kernel_options": used_options,
+                     "note": "torch.compile(flex_attention) fwd+bwd, block mask built once outside the timed region"}})
+
+
 _REAL_STDOUT = None
 
 
@@ -465,7 +535,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "flex_gpu"],
+                    help="ours: this package's CUDA path.  reference: the reference's CPU path on a bounded sample.  "
+                         "flex_gpu: PyTorch FlexAttention (the reference's GPU path) on the same inputs, single GPU.")
     ap.add_argument("--no-train", action="store_true", help="skip the short training-step measurement appended to the 32k line")
     ap.add_argument("--workload", default="32k", choices=["32k", "16k", "train4", "train5"],
                     help="32k: the headline mask sweep (default).  16k: B=1, T=16384, H=16, cross_doc_link p=0.15 "
@@ -488,7 +560,10 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         torch.distributed.init_process_group("nccl", device_id=device)
     try:
-        if args.workload in ("train4", "train5"):
+        if args.impl == "flex_gpu":
+            if rank == 0:
+                run_flex_gpu(args, rank, 1, device)
+        elif args.workload in ("train4", "train5"):
             res = run_train(args, rank, world, device, args.workload, steps=args.steps, warmup=max(3, args.warmup))
             if rank == 0:
                 res.update({"n_gpus": world, "warmup": max(3, args.warmup), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
