@@ -101,7 +101,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint8_t* sQ = smem;
   uint8_t* sK = smem + Cfg::kTileBytes;
   uint8_t* sV = smem + 2 * Cfg::kTileBytes;
-  __shared__ uint64_t bar_q, bar_k, bar_v, bar_s, bar_p, bar_o, bar_epi, bar_mx, bar_l;
+  __shared__ uint64_t bar_q, bar_k, bar_v, bar_s, bar_p, bar_o, bar_epi, bar_mx[4], bar_l;
   __shared__ float s_mx[2][2][kTile];  // [tile parity][column half][row]: half-row maxima
   __shared__ float s_l[2][kTile];      // [column half][row]: half-row sums, exchanged once at the end
   __shared__ uint32_t tmem_slot;
@@ -138,7 +138,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     mbar_init(&bar_p, 2 * kTile);
     mbar_init(&bar_o, 1);
     mbar_init(&bar_epi, 2 * kTile);
-    mbar_init(&bar_mx, 2 * kTile);
+    for (int i = 0; i < 4; ++i) mbar_init(&bar_mx[i], 64);  // one per pair of warps that share 32 query rows
     mbar_init(&bar_l, 2 * kTile);
     fence_mbar_init();
   }
@@ -261,8 +261,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       }
       float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
       s_mx[j & 1][half][row] = mx;
-      mbar_arrive(&bar_mx);
-      if (!(ok = mbar_wait(&bar_mx, j & 1, &abort_word, 34))) break;
+      mbar_arrive(&bar_mx[warp & 3]);
+      if (!(ok = mbar_wait(&bar_mx[warp & 3], j & 1, &abort_word, 34))) break;
       mx = fmaxf(mx, s_mx[j & 1][half ^ 1][row]);
       if (tid == 0) FTRACE(1, j, 2);
       mx *= p.scale_log2;  // scale > 0, so max commutes with the scaling
