@@ -45,47 +45,65 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """SM clock and throttle reasons sampled every 50 ms while the timed region runs, read-only through NVML in a
+    background thread (spawning nvidia-smi inside the timed region was measured to stall the GPU for tens of
+    milliseconds per poll); falls back to one nvidia-smi query after the region when NVML is unavailable."""
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
     def __init__(self, index: int):
-        self.index, self.proc = index, None
+        self.index = index
+        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        self._stop = False
+        self._thread = None
+        self._sm, self._reasons, self._max = [], set(), None
+
+    def _physical_index(self) -> int:
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [x.strip() for x in vis.split(",") if x.strip()]
+            if self.index < len(ids) and ids[self.index].isdigit():
+                return int(ids[self.index])
+        return self.index
+
+    def _loop(self, nv, handle):
+        while not self._stop:
+            try:
+                self._sm.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(handle))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self._reasons.add(name)
+            except Exception:  # noqa: BLE001 - sampling must never disturb the measurement
+                break
+            time.sleep(0.05)
 
     def __enter__(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+            import pynvml as nv
+            import threading
+            nv.nvmlInit()
+            handle = nv.nvmlDeviceGetHandleByIndex(self._physical_index())
+            self._max = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+            self._thread = threading.Thread(target=self._loop, args=(nv, handle), daemon=True)
+            self._thread.start()
+        except Exception:  # noqa: BLE001
+            self._thread = None
         return self
 
     def __exit__(self, *exc):
-        self.result = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
-        if self.proc is None:
+        self._stop = True
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+        if self._sm:
+            self.result = {"sm_mhz": statistics.median(self._sm), "sm_max_mhz": self._max, "reasons": sorted(self._reasons),
+                           "samples": len(self._sm), "source": "nvml"}
             return
-        time.sleep(0.25)
-        self.proc.terminate()
-        try:
-            out, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            out = ""
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in out.strip().splitlines():
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0])); mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        if sm:
-            self.result = {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        try:  # fallback: a single query after the region
+            out = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm", "--format=csv,noheader,nounits", "-i", str(self.index)],
+                                 capture_output=True, text=True, timeout=20).stdout.strip().split(",")
+            self.result = {"sm_mhz": float(out[0]), "sm_max_mhz": float(out[1]), "reasons": [], "samples": 1, "source": "nvidia-smi after the region"}
+        except Exception:  # noqa: BLE001
+            pass
 
 
 def make_workload(rank: int, device):
@@ -159,7 +177,7 @@ def run_ours(args, rank, world, device):
     fms, bms = ctypes.c_float(0), ctypes.c_float(0)
     for m in masks:
         f_list, b_list = [], []
-        for _ in range(max(3, min(args.steps, 10))):
+        for _ in range(max(3, min(args.steps, 5))):
             bm = build_block_map(m["doc"], m["link"])
             out, lse = _attn_fwd(q, k, v, m["doc"], m["link"], None, None, bm.plan, scale)
             _attn_bwd(q, k, v, out, do, lse, m["doc"], m["link"], None, None, bm.plan, scale)
@@ -533,7 +551,7 @@ def main():
     os.dup2(2, 1)  # libraries that print to fd 1 (e.g. the NCCL version banner) must not pollute the JSON line
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "flex_gpu"],
                     help="ours: this package's CUDA path.  reference: the reference's CPU path on a bounded sample.  "
