@@ -50,3 +50,36 @@ def forward_backward(q, k, v, dense, dout, scale: Optional[float] = None):
     dq = torch.matmul(ds, k) * scale
     dk = torch.matmul(ds.transpose(-1, -2), q) * scale
     return out, lse, dq, dk, dv
+
+
+def forward_backward_streamed(q, k, v, dout, slab_mask, scale: Optional[float] = None, slab: int = 2048):
+    """Same math as ``forward_backward`` for ONE (batch, head) slice q,k,v,dout [T,D], evaluated in slabs of query rows so
+    that a 32k-token sequence needs [slab, T] scores at a time.  ``slab_mask(q0, q1)`` returns the bool mask [q1-q0, T]
+    of those rows.  Runs on whatever device the inputs live on (fp32; keep TF32 matmuls off).
+    Returns (out [T,D], lse [T], dq, dk, dv)."""
+    q, k, v, dout = q.float(), k.float(), v.float(), dout.float()
+    t, d = q.shape
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    out = torch.empty_like(q)
+    lse = torch.empty(t, dtype=torch.float32, device=q.device)
+    dq = torch.empty_like(q)
+    dk = torch.zeros_like(k)
+    dv = torch.zeros_like(v)
+    for q0 in range(0, t, slab):
+        q1 = min(t, q0 + slab)
+        m = slab_mask(q0, q1)
+        s = (q[q0:q1] @ k.T) * scale
+        s = s.masked_fill(~m, float("-inf"))
+        l = torch.logsumexp(s, dim=-1)
+        dead = torch.isinf(l)
+        p = torch.exp(s - torch.where(dead, torch.zeros_like(l), l)[:, None])
+        p = torch.where(dead[:, None], torch.zeros_like(p), p)
+        o = p @ v
+        out[q0:q1], lse[q0:q1] = o, l
+        do = dout[q0:q1]
+        delta = (o * do).sum(-1, keepdim=True)
+        dv += p.T @ do
+        ds = p * (do @ v.T - delta)
+        dq[q0:q1] = (ds @ k) * scale
+        dk += (ds.T @ q[q0:q1]) * scale
+    return out, lse, dq, dk, dv

@@ -171,6 +171,48 @@ def test_full_size_config2_one_head_against_gpu_evaluated_oracle():
         assert (q.grad[:, h].float() - q.grad[:, 0].float()).abs().max().item() <= 2e-2
 
 
+def test_full_size_32k_one_head_against_streamed_gpu_oracle_and_properties():
+    """The headline size: B=2, T=32768, H=16, D=128, cross_doc_link p=0.3 packs.  One (batch, head) slice is checked
+    against the oracle math evaluated in fp32 on the GPU in slabs of 2048 query rows (the dense scores of one slab are
+    268 MB); all slices are checked through size-independent properties: V = 1 gives O = 1, and dV is linear in dO."""
+    from tagseq2tagseq_b200 import build_block_map, read_status, synth
+    from tagseq2tagseq_b200.attention import _attn_bwd, _attn_fwd
+    torch.backends.cuda.matmul.allow_tf32 = False
+    dev = torch.device("cuda")
+    packs = [synth.config3_pack(1023 + b, "link_p30") for b in range(2)]
+    doc_np, link_np = synth.stack_packs(packs)
+    doc, link = torch.from_numpy(doc_np).to(dev), torch.from_numpy(link_np).to(dev)
+    bm = build_block_map(doc, link)
+    g = torch.Generator(device=dev).manual_seed(3)
+    B, H, T, D = 2, 16, 32768, 128
+    q, k, v, do = (torch.randn(B, H, T, D, device=dev, generator=g).bfloat16() for _ in range(4))
+    scale = D ** -0.5
+    out, lse = _attn_fwd(q, k, v, doc, link, None, None, bm.plan, scale)
+    dq, dk, dv = _attn_bwd(q, k, v, out, do, lse, doc, link, None, None, bm.plan, scale)
+    torch.cuda.synchronize()
+    assert read_status(bm.plan) == 0
+    b, h = 1, 5
+    doc_b, link_b = doc_np[b], link_np[b]
+
+    def slab_mask(q0, q1):
+        return torch.from_numpy(om.class_mask_dense(doc_b, None, None, link_b, q_range=(q0, q1))).to(dev)
+
+    ro, rl, rdq, rdk, rdv = oattn.forward_backward_streamed(q[b, h], k[b, h], v[b, h], do[b, h], slab_mask, scale)
+    assert (out[b, h].float() - ro).abs().max().item() <= O_TOL
+    assert (lse[b, h] - rl).abs().max().item() <= LSE_TOL
+    for a, r in ((dq[b, h], rdq), (dk[b, h], rdk), (dv[b, h], rdv)):
+        assert ((a.float() - r).norm() / r.norm()).item() <= GRAD_TOL
+    # properties over every slice
+    ones = torch.ones_like(v)
+    o1, l1 = _attn_fwd(q, k, ones, doc, link, None, None, bm.plan, scale)
+    assert (o1.float() - 1.0).abs().max().item() <= 1e-2 and torch.equal(l1, lse)
+    do2 = torch.randn(B, H, T, D, device=dev, generator=g).bfloat16()
+    _, _, dv2 = _attn_bwd(q, k, v, out, do2, lse, doc, link, None, None, bm.plan, scale)
+    _, _, dv12 = _attn_bwd(q, k, v, out, (do.float() + do2.float()).bfloat16(), lse, doc, link, None, None, bm.plan, scale)
+    lin = (dv12.float() - dv.float() - dv2.float()).norm() / dv12.float().norm()
+    assert lin.item() <= 1e-2
+
+
 def test_argument_errors():
     from tagseq2tagseq_b200.attention import masked_attn
     dev = torch.device("cuda")

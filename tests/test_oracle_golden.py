@@ -120,3 +120,15 @@ def test_class_mask_reproduces_doc_level_links():
         for ki in range(t):
             exp = qi >= ki and (ids[qi] == ids[ki] or bool((link[ids[qi], 0] >> ids[ki]) & 1))
             assert dense[qi, ki] == exp
+
+
+def test_streamed_oracle_equals_dense_oracle():
+    g = torch.Generator().manual_seed(9)
+    t, d = 300, 32
+    q, k, v, do = (torch.randn(t, d, generator=g) for _ in range(4))
+    dense = torch.tril(torch.ones(t, t, dtype=torch.bool)) & (torch.rand(t, t, generator=g) > 0.3)
+    dense |= torch.eye(t, dtype=torch.bool)
+    ref = oattn.forward_backward(q[None, None], k[None, None], v[None, None], dense, do[None, None])
+    got = oattn.forward_backward_streamed(q, k, v, do, lambda a, b: dense[a:b], slab=64)
+    for a, b in zip(got, ref):
+        assert torch.allclose(a, b[0, 0], atol=1e-5, rtol=1e-5)
