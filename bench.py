@@ -302,9 +302,16 @@ def run_train(args, rank, world, device, which: str, steps: int, warmup: int):
     from tagseq2tagseq_b200.train_step import TrainStep, config4, config5, train_flops_per_step
     cfg, t_len, base = (config4(), 16384, 1004) if which == "train4" else (config5(), 32768, 1005)
     ts = TrainStep(cfg, device, world)
-    n_packs = 4  # a small rotation of packs per rank, all resident on the device
-    packs = [synth.config2_pack(rank_seed(base, rank, i)) if which == "train4" else synth.config5_pack(rank_seed(base, rank, i))
-             for i in range(n_packs)]
+    n_packs = 4  # steps in the pool; every rank derives the same pool of world * n_packs packs from the seeds
+    from tagseq2tagseq_b200.replicas import schedule_packs
+    make = (lambda sd: synth.config2_pack(sd)) if which == "train4" else (lambda sd: synth.config5_pack(sd))
+    pool = [make(rank_seed(base, r, i)) for i in range(n_packs) for r in range(world)]
+    if args.no_balance:
+        mine = [i * world + rank for i in range(n_packs)]
+    else:  # packs of similar attention cost share a step, so that no rank waits long for the slowest one
+        sched = schedule_packs([float(pk.unmasked_pairs()) for pk in pool], world)
+        mine = [sched[i][rank] for i in range(n_packs)]
+    packs = [pool[i] for i in mine]
     g = torch.Generator().manual_seed(rank_seed(base, rank))
     batches = []
     for pk in packs:
@@ -335,7 +342,8 @@ def run_train(args, rank, world, device, which: str, steps: int, warmup: int):
     peak_tf, _, kind = measured_peaks()
     return {"metric": "train tokens/s", "value": tot_tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms / steps, "steps": steps,
             "model": f"{cfg.n_layers}L d{cfg.d_model} {cfg.n_heads}h hd{cfg.head_dim} swiglu{cfg.mlp_hidden} V{cfg.vocab}",
-            "seq_len": t_len, "global_batch_tokens": t_len * world, "parallelism": f"ddp{world}", "optimizer": "fused AdamW (fp32 params, bf16 autocast)",
+            "seq_len": t_len, "global_batch_tokens": t_len * world, "parallelism": f"ddp{world}", "pack_schedule": "seed order" if args.no_balance else "density-aware (similar-cost packs share a step)",
+            "optimizer": "fused AdamW (fp32 params, bf16 autocast)",
             "model_tflops": tot_flops / (ms * 1e-3) / 1e12, "frac_of_peak": tot_flops / (ms * 1e-3) / 1e12 / (peak_tf * world),
             "peak_kind": kind, "loss": float(loss)}
 
@@ -556,6 +564,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference", "flex_gpu"],
                     help="ours: this package's CUDA path.  reference: the reference's CPU path on a bounded sample.  "
                          "flex_gpu: PyTorch FlexAttention (the reference's GPU path) on the same inputs, single GPU.")
+    ap.add_argument("--no-balance", action="store_true", help="training step: keep the seed order of packs instead of the density-aware schedule")
     ap.add_argument("--no-train", action="store_true", help="skip the short training-step measurement appended to the 32k line")
     ap.add_argument("--workload", default="32k", choices=["32k", "16k", "train4", "train5"],
                     help="32k: the headline mask sweep (default).  16k: B=1, T=16384, H=16, cross_doc_link p=0.15 "

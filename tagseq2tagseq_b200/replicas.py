@@ -27,3 +27,30 @@ def aggregate(elapsed_ms: Sequence[float], work: Sequence[float], device=None) -
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dist.all_reduce(w, op=dist.ReduceOp.SUM)
     return t.tolist(), w.tolist()
+
+
+def schedule_packs(costs: Sequence[float], world: int) -> list:
+    """Density-aware pack -> (step, rank) schedule.
+
+    With one packed sequence per rank per step, a DDP step lasts as long as its most expensive pack, and attention
+    cost varies several-fold between packs (the reference reports backward times of 2-6 s across ranks,
+    configs/stack_100m_32k_baseline.yaml:39-41, and lists balancing as an open item, README.md:151).  Given the
+    cost of every pack in a pool of ``steps * world`` packs (e.g. non-skipped tiles from the block-map pre-pass, or
+    the exact number of unmasked pairs), packs of similar cost are put into the same step: sort by cost and cut into
+    consecutive groups of ``world``.  Within a step the ranks are rotated so that no rank always gets the largest.
+    Every rank computes the same schedule from the same costs, so no communication is needed.
+
+    Returns ``schedule[step][rank] = pack index``; packs beyond a multiple of ``world`` are dropped."""
+    order = sorted(range(len(costs)), key=lambda i: (-costs[i], i))
+    steps = len(order) // world
+    sched = []
+    for s in range(steps):
+        group = order[s * world:(s + 1) * world]
+        rot = s % world
+        sched.append(group[rot:] + group[:rot])
+    return sched
+
+
+def step_time_model(costs: Sequence[float], schedule: Sequence[Sequence[int]]) -> float:
+    """Sum over steps of the most expensive pack in the step (what the slowest rank makes every other rank wait for)."""
+    return float(sum(max(costs[i] for i in step) for step in schedule))

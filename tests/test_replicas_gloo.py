@@ -52,3 +52,19 @@ def test_aggregate_without_process_group_is_identity():
     from tagseq2tagseq_b200.replicas import aggregate, rank_seed
     assert aggregate([3.0], [7.0]) == ([3.0], [7.0])
     assert rank_seed(1003, 2, 1) == 3004
+
+
+def test_density_aware_schedule_reduces_the_slowest_rank_stall():
+    from tagseq2tagseq_b200 import synth
+    from tagseq2tagseq_b200.replicas import schedule_packs, step_time_model
+    world, steps = 8, 6
+    costs = [float(synth.make_pack(500 + i, 8192, 150, 16, 4096, p_link=0.15, heavy_frac=0.05, heavy_lo=2048, heavy_hi=4096).unmasked_pairs())
+             for i in range(world * steps)]
+    naive = [list(range(s * world, (s + 1) * world)) for s in range(steps)]
+    sched = schedule_packs(costs, world)
+    assert sorted(i for st in sched for i in st) == list(range(world * steps))      # every pack used exactly once
+    assert all(len(st) == world for st in sched)
+    assert step_time_model(costs, sched) <= step_time_model(costs, naive)
+    assert step_time_model(costs, sched) < 0.9 * step_time_model(costs, naive)       # heavy-tailed packs: a clear gain
+    lower_bound = sum(costs) / world
+    assert step_time_model(costs, sched) >= lower_bound
