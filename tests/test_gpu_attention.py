@@ -226,3 +226,47 @@ def test_argument_errors():
         masked_attn(x.cpu(), x.cpu(), x.cpu(), doc)
     with pytest.raises(ValueError):
         masked_attn(x, x, x, doc, scale=-1.0)
+
+
+def test_kernel_timing_hooks_and_plan_checks():
+    """ts2ts_profile_enable / ts2ts_profile_last_ms bracket the main kernels; a plan that is too small is refused."""
+    import ctypes
+    from tagseq2tagseq_b200 import _lib, build_block_map, synth
+    from tagseq2tagseq_b200.attention import _attn_bwd, _attn_fwd
+    L = _lib.lib()
+    dev = torch.device("cuda")
+    pack = synth.make_pack(2, 2048, 100, 8, 600, p_link=0.2)
+    doc = torch.from_numpy(pack.doc_ids)[None].to(dev)
+    link = torch.from_numpy(pack.link_bits)[None].to(dev)
+    plan = build_block_map(doc, link).plan
+    q, k, v, do = (torch.randn(1, 2, 2048, 64, device=dev).bfloat16() for _ in range(4))
+    ms = ctypes.c_float(-1.0)
+    assert L.ts2ts_profile_last_ms(0, ctypes.byref(ms)) != 0          # nothing recorded yet / profiling off
+    assert L.ts2ts_profile_enable(1) == 0
+    out, lse = _attn_fwd(q, k, v, doc, link, None, None, plan, 0.125)
+    _attn_bwd(q, k, v, out, do, lse, doc, link, None, None, plan, 0.125)
+    assert L.ts2ts_profile_last_ms(0, ctypes.byref(ms)) == 0 and 0.0 < ms.value < 100.0
+    assert L.ts2ts_profile_last_ms(1, ctypes.byref(ms)) == 0 and 0.0 < ms.value < 100.0
+    assert L.ts2ts_profile_enable(0) == 0
+    small = plan[: plan.numel() // 2].contiguous()
+    with pytest.raises(_lib.Ts2tsError, match="plan buffer too small"):
+        _attn_fwd(q, k, v, doc, link, None, None, small, 0.125)
+
+
+def test_flex_shim_broadcasts_a_single_mask_over_the_batch():
+    """The reference builds one mask per micro-batch with B=None broadcast (block_mask_creator.py:132-139)."""
+    from tagseq2tagseq_b200 import MaskSpec, synth
+    from tagseq2tagseq_b200.attention import flex_attention
+    dev = torch.device("cuda")
+    pack = synth.make_pack(8, 600, 50, 4, 200, p_link=0.3)
+    spec = MaskSpec(doc_ids=torch.from_numpy(pack.doc_ids)[None].to(dev), link_bits=torch.from_numpy(pack.link_bits)[None].to(dev))
+    g = torch.Generator().manual_seed(4)
+    q, k, v = (torch.randn(3, 2, 600, 64, generator=g).bfloat16() for _ in range(3))
+    out = flex_attention(q.to(dev), k.to(dev), v.to(dev), block_mask=spec)
+    dense = torch.from_numpy(om.class_mask_dense(pack.doc_ids, None, None, pack.link_bits))
+    ref, _ = oattn.forward(q, k, v, dense)
+    assert (out.float().cpu() - ref).abs().max().item() <= O_TOL
+    with pytest.raises(NotImplementedError):
+        flex_attention(q.to(dev), k.to(dev), v.to(dev), score_mod=lambda s, b, h, qi, ki: s, block_mask=spec)
+    with pytest.raises(TypeError):
+        flex_attention(q.to(dev), k.to(dev), v.to(dev), block_mask=None)
