@@ -176,15 +176,18 @@ def run_ours(args, rank, world, device):
     per_mask = []
     fms, bms = ctypes.c_float(0), ctypes.c_float(0)
     for m in masks:
-        f_list, b_list = [], []
+        f_list, b_list, pp_list = [], [], []
         for _ in range(max(3, min(args.steps, 5))):
+            pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            pe0.record()
             bm = build_block_map(m["doc"], m["link"])
+            pe1.record()
             out, lse = _attn_fwd(q, k, v, m["doc"], m["link"], None, None, bm.plan, scale)
             _attn_bwd(q, k, v, out, do, lse, m["doc"], m["link"], None, None, bm.plan, scale)
             L.ts2ts_profile_last_ms(0, ctypes.byref(fms)); L.ts2ts_profile_last_ms(1, ctypes.byref(bms))
-            f_list.append(fms.value); b_list.append(bms.value)
+            f_list.append(fms.value); b_list.append(bms.value); pp_list.append(pe0.elapsed_time(pe1))
         per_mask.append({"mask": m["name"], "density": round(m["density"], 4), "fwd_ms": statistics.mean(f_list),
-                         "bwd_ms": statistics.mean(b_list), "fwd_tflops": 4.0 * D * H * m["pairs"] / statistics.mean(f_list) / 1e9,
+                         "bwd_ms": statistics.mean(b_list), "prepass_ms": statistics.median(pp_list), "fwd_tflops": 4.0 * D * H * m["pairs"] / statistics.mean(f_list) / 1e9,
                          "bwd_tflops": 10.0 * D * H * m["pairs"] / statistics.mean(b_list) / 1e9})
     L.ts2ts_profile_enable(0)
     bwd_flops = sum(10.0 * D * H * m["pairs"] for m in masks) / len(masks)

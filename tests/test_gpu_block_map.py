@@ -101,3 +101,28 @@ def test_rejects_bad_arguments():
         build_block_map(torch.zeros((1, 8), dtype=torch.int32))
     with pytest.raises(ValueError):
         build_block_map(torch.zeros((1, 8), dtype=torch.int32, device=dev), torch.zeros((2, 1, 1), dtype=torch.int64, device=dev))
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_fuzz_random_classes_and_ragged_lengths(seed):
+    """Random doc runs with random row / column classes (including -1 and out-of-range values) and random link
+    bits, at lengths around tile boundaries."""
+    from tagseq2tagseq_b200 import build_block_map
+    rng = np.random.default_rng(900 + seed)
+    t = int(rng.choice([65, 128, 255, 257, 511, 640, 1000, 1283]))
+    def runs(values, mean_len):
+        out = []
+        while len(out) < t:
+            out += [int(rng.choice(values))] * int(rng.integers(1, mean_len))
+        return np.asarray(out[:t], dtype=np.int32)
+    doc = runs(list(range(-2, 9)), 90)
+    row = runs([-1, 0, 1, 2, 3, 4, 5, 6, 9], 70)      # 9 is out of range for R = 7
+    col = runs([-1, 0, 1, 2, 63, 64, 65, 127, 200], 50)  # 200 is out of range for W = 2
+    link = rng.integers(-2**63, 2**63 - 1, size=(7, 2), dtype=np.int64)
+    link[rng.random((7, 2)) < 0.4] = 0
+    dev = torch.device("cuda")
+    bm = build_block_map(torch.from_numpy(doc)[None].to(dev), torch.from_numpy(link)[None].to(dev),
+                         torch.from_numpy(row)[None].to(dev), torch.from_numpy(col)[None].to(dev), with_lists=True)
+    st = obm.block_states(om.class_mask_dense(doc, row, col, link))
+    assert np.array_equal(bm.state[0].cpu().numpy(), st)
+    _check_lists(bm, st)

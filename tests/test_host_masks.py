@@ -76,3 +76,37 @@ def test_synthetic_generator_is_seeded_and_counts_pairs():
     assert p1.seq_len == 2048 and p1.link_bits is None
     doc, link = synth.stack_packs([synth.make_pack(1, 512, 50, 4, 100, p_link=0.5), synth.make_pack(2, 512, 20, 4, 100, p_link=0.5)])
     assert doc.shape == (2, 512) and link.shape[0] == 2 and link.dtype == np.int64
+
+
+@pytest.mark.parametrize("seed", range(60))
+def test_fuzz_reference_format_adapter_against_oracle(seed):
+    """Random spans (gaps, clipping, repeated doc ids), random links (several targets per position, unknown targets,
+    positions outside every span) and random caps: the adapter's (row, col, link bits) must give the same mask as the
+    oracle's restatement of the reference bitmask construction."""
+    from types import SimpleNamespace
+    rng = np.random.default_rng(7000 + seed)
+    n_docs = int(rng.integers(1, 12))
+    spans, pos = [], -int(rng.integers(0, 4))
+    for d in range(n_docs):
+        pos += int(rng.choice([0, 0, 1, 4]))
+        w = int(rng.integers(1, 60))
+        doc_id = d if rng.random() > 0.1 else int(rng.integers(0, max(1, d)))  # occasionally a repeated id
+        spans.append(SimpleNamespace(doc_id=doc_id, start=pos, end=pos + w, raw_identifier=f"d{d}"))
+        pos += w
+    seq_len = max(1, pos - int(rng.choice([0, 0, 3, 17])))
+    links = {}
+    for _ in range(int(rng.integers(0, 40))):
+        lp = int(rng.integers(0, pos + 3))
+        links.setdefault(lp, []).append(int(rng.integers(0, n_docs + 1)))
+    max_grants = int(rng.choice([64, 128, 256]))
+    cap = int(rng.choice([max_grants, max_grants, 3, 1, 10]))
+    ids = ms.build_document_ids(seq_len, spans)
+    qb, kb = om.grant_bitmasks(seq_len, spans, links, max_grants=max_grants, cap=cap)
+    ref = om.cross_doc_link_dense(om.document_ids(seq_len, spans), qb, kb)
+    grants = ms.ordered_grants(seq_len, spans, links, cap)
+    if grants:
+        row, col, link = ms.grant_classes(seq_len, grants)
+        mine = om.class_mask_dense(ids, row, col, link)
+    else:
+        mine = om.doc_causal_dense(ids)
+    assert np.array_equal(mine, ref)
