@@ -270,3 +270,24 @@ def test_flex_shim_broadcasts_a_single_mask_over_the_batch():
         flex_attention(q.to(dev), k.to(dev), v.to(dev), score_mod=lambda s, b, h, qi, ki: s, block_mask=spec)
     with pytest.raises(TypeError):
         flex_attention(q.to(dev), k.to(dev), v.to(dev), block_mask=None)
+
+
+def test_backward_is_reproducible_except_for_dq_rounding_order():
+    """dk and dv are accumulated in tensor memory in a fixed order: bit-identical run to run.  dq is reduced with
+    fp32 additions in L2 whose order varies: identical up to one bf16 rounding step."""
+    from tagseq2tagseq_b200 import build_block_map, synth
+    from tagseq2tagseq_b200.attention import _attn_bwd, _attn_fwd
+    dev = torch.device("cuda")
+    pack = synth.make_pack(31, 4096, 300, 32, 3000, p_link=0.2)
+    doc = torch.from_numpy(pack.doc_ids)[None].to(dev)
+    link = torch.from_numpy(pack.link_bits)[None].to(dev)
+    plan = build_block_map(doc, link).plan
+    g = torch.Generator(device=dev).manual_seed(6)
+    q, k, v, do = (torch.randn(1, 4, 4096, 128, device=dev, generator=g).bfloat16() for _ in range(4))
+    out, lse = _attn_fwd(q, k, v, doc, link, None, None, plan, 128 ** -0.5)
+    first = _attn_bwd(q, k, v, out, do, lse, doc, link, None, None, plan, 128 ** -0.5)
+    for _ in range(5):
+        dq, dk, dv = _attn_bwd(q, k, v, out, do, lse, doc, link, None, None, plan, 128 ** -0.5)
+        assert torch.equal(dk, first[1]) and torch.equal(dv, first[2])
+        scale = first[0].float().abs().clamp_min(1e-3)
+        assert ((dq.float() - first[0].float()).abs() / scale).max().item() <= 2 ** -6
