@@ -97,7 +97,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
                 const __grid_constant__ CUtensorMap mapV, const __grid_constant__ CUtensorMap mapO, const FwdParams p) {
   using Cfg = FwdSmem<D>;
   extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // Plain pointer arithmetic (no round trip through an integer) keeps the shared address space visible to the
+  // compiler, so every access below becomes a shared-memory instruction instead of a generic one.
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   uint8_t* sQ = smem;
   uint8_t* sK = smem + Cfg::kTileBytes;
   uint8_t* sV = smem + 2 * Cfg::kTileBytes;
