@@ -107,21 +107,28 @@ __device__ __forceinline__ void allowed_rows(const PlanView& P, const MaskArgs& 
   }
 }
 
-// One 32-column chunk of a sub-step: P^T and dS^T (packed bf16 pairs) from S^T, dP^T, the row statistics and the mask.
-// One 32-column chunk of a sub-step: P^T and dS^T (packed bf16 pairs) from S^T, dP^T, the row statistics (already in
-// registers: they do not depend on the MMA results and are fetched while waiting for them) and the mask.
-__device__ __forceinline__ void pds_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], const float (&l2)[32], const float (&dl)[32],
+// One 32-column chunk of a sub-step: P^T and dS^T (packed bf16 pairs) from S^T, dP^T, the row statistics of the 32
+// queries (read from shared memory; every lane of a warp reads the same addresses) and the mask.
+__device__ __forceinline__ void pds_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], const float* l2, const float* dl,
                                           uint32_t bw, bool masked, float scale_log2, uint32_t* pk, uint32_t* dsk) {
 #pragma unroll
-  for (int e = 0; e < 32; e += 2) {
-    float p0 = fast_exp2(fmaf(__uint_as_float(s[e + 0]), scale_log2, -l2[e + 0]));
-    float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), scale_log2, -l2[e + 1]));
+  for (int e = 0; e < 32; e += 4) {
+    const float4 l4 = *reinterpret_cast<const float4*>(l2 + e);
+    const float4 d4 = *reinterpret_cast<const float4*>(dl + e);
+    float p0 = fast_exp2(fmaf(__uint_as_float(s[e + 0]), scale_log2, -l4.x));
+    float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), scale_log2, -l4.y));
+    float p2 = fast_exp2(fmaf(__uint_as_float(s[e + 2]), scale_log2, -l4.z));
+    float p3 = fast_exp2(fmaf(__uint_as_float(s[e + 3]), scale_log2, -l4.w));
     if (masked) {
       p0 = ((bw >> (e + 0)) & 1u) ? p0 : 0.f;
       p1 = ((bw >> (e + 1)) & 1u) ? p1 : 0.f;
+      p2 = ((bw >> (e + 2)) & 1u) ? p2 : 0.f;
+      p3 = ((bw >> (e + 3)) & 1u) ? p3 : 0.f;
     }
-    pk[e >> 1] = pack_bf16(p0, p1);
-    dsk[e >> 1] = pack_bf16(p0 * (__uint_as_float(dp[e + 0]) - dl[e + 0]), p1 * (__uint_as_float(dp[e + 1]) - dl[e + 1]));
+    pk[(e >> 1) + 0] = pack_bf16(p0, p1);
+    pk[(e >> 1) + 1] = pack_bf16(p2, p3);
+    dsk[(e >> 1) + 0] = pack_bf16(p0 * (__uint_as_float(dp[e + 0]) - d4.x), p1 * (__uint_as_float(dp[e + 1]) - d4.y));
+    dsk[(e >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dp[e + 2]) - d4.z), p3 * (__uint_as_float(dp[e + 3]) - d4.w));
   }
 }
 
@@ -215,7 +222,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   // P^T bf16 [.., +16) and dS^T bf16 [.. + 16, +16) for its 32 queries.
 
   if (warp >= 12) {
-    reg_dec<56>();
+    reg_dec<88>();
     if (warp == 12 && lane == 0) {
       // ---------------------------------------------------------------- TMA producer
       tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV); tma_prefetch_desc(&mapDO);
@@ -321,7 +328,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ exp / dS warps: thread = (key row, 32 of 64 queries)
-    reg_inc<152>();
+    reg_dec<120>();
     const int row = tid & (kTile - 1), half = tid >> 7;
     const int kv = kb * kTile + row;
     const bool kv_valid = kv < P.T;
@@ -349,18 +356,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       if (!(ok = mbar_wait(&bar_qdo_full[st], (i >> 1) & 1, abort_w, 30))) break;  // lse2 / delta of this tile landed
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
-        // row statistics of this thread's 32 queries: fetched before waiting for the MMAs they do not depend on
-        float l2[32], dl[32];
-        {
-          const float4* pl = reinterpret_cast<const float4*>(s_lse2[st] + s * kSubQ + 32 * half);
-          const float4* pd = reinterpret_cast<const float4*>(s_delta[st] + s * kSubQ + 32 * half);
-#pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float4 a4 = pl[e], b4 = pd[e];
-            l2[4 * e] = a4.x; l2[4 * e + 1] = a4.y; l2[4 * e + 2] = a4.z; l2[4 * e + 3] = a4.w;
-            dl[4 * e] = b4.x; dl[4 * e + 1] = b4.y; dl[4 * e + 2] = b4.z; dl[4 * e + 3] = b4.w;
-          }
-        }
         if (s == 0 && !(ok = mbar_wait(&bar_st, i & 1, abort_w, 31))) break;
         tc_fence_after();
         if (tid == 0) TRACE(1, i, 4 * s + 0);
@@ -371,7 +366,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tmem_ld_wait();
         if (tid == 0) TRACE(1, i, 4 * s + 1);
         const uint32_t bw = s == 0 ? (half == 0 ? bits[0] : bits[1]) : (half == 0 ? bits[2] : bits[3]);
-        pds_chunk(sv, dp, l2, dl, bw, masked, p.scale_log2, pk, dsk);
+        pds_chunk(sv, dp, s_lse2[st] + s * kSubQ + 32 * half, s_delta[st] + s * kSubQ + 32 * half, bw, masked, p.scale_log2, pk, dsk);
         if (tid == 0) TRACE(1, i, 4 * s + 2);
         tmem_st16(tST + col, pk);
         tmem_st16(tST + col + 16, dsk);
@@ -427,7 +422,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------------ dQ reduction warps 8-11, thread = head-dim lane
-    reg_inc<152>();
+    reg_inc<168>();
     const int dlane = tid - 2 * kTile;  // 0..127 = TMEM lane = index into D
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     // Each warp owns one 128-byte-swizzled fp32 box of [128 queries x 32 floats]: box d/32 lives in the Q stage
