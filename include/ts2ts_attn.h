@@ -116,6 +116,24 @@ int ts2ts_attn_bwd_noalloc(const void* q, const void* k, const void* v, const vo
                            size_t plan_bytes, void* dq, void* dk, void* dv, const int64_t* dq_strides,
                            const int64_t* dk_strides, const int64_t* dv_strides, void* stream);
 
+/* Candidate markdown links "[text](target)" of one token sequence, found on the device.  Replaces the scan of
+ * MarkdownLinkDetector.detect_links (model/graph_traversal/markdown_link_detector.py:57-108), which reads tokens
+ * one by one on the host:
+ *   tokens       device, int32[T] (token_bytes = 4) or int64[T] (token_bytes = 8)
+ *   mid_id       id of the "](" token (`:45`); start_ids / n_start (<= 8): ids that can be "[" (`:43-44`), host array
+ *   close_flags  device uint8[vocab]: 1 when the token's bytes contain ')'
+ *   back_limit   how far back "[" is looked for (100 in the reference, `:74`); window: `window_tokens` (`:88`)
+ *   scratch      device, ts2ts_detect_links_scratch_bytes(T) bytes, 16-byte aligned
+ *   links        device int32[max_links][3]: (position of "](", position of "[", position of the token that closes the
+ *                link), ascending by position -- the order in which the reference appends its links
+ *   count        device int32: candidates found (may exceed max_links; only max_links triples are stored)
+ * A "](" without "[" in reach or without a closing token inside the window gives no triple, as in the reference.
+ * Decoding the target tokens (positions mid+1 .. close) and the non-empty test (`:94-97`) stay with the caller. */
+size_t ts2ts_detect_links_scratch_bytes(int T);
+int ts2ts_detect_links(const void* tokens, int token_bytes, int T, int64_t mid_id, const int64_t* start_ids, int n_start,
+                       const uint8_t* close_flags, int vocab, int back_limit, int window, void* scratch,
+                       size_t scratch_bytes, int32_t* links, int max_links, int32_t* count, void* stream);
+
 /* Waits for `stream`, then copies the plan's device status word to *status_out (host).
  * 0 = every kernel that used this plan since the last ts2ts_block_map ran to completion. */
 int ts2ts_read_status(const void* plan, void* stream, int32_t* status_out);

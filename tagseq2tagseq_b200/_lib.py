@@ -27,6 +27,9 @@ SYMBOLS = {
     "ts2ts_attn_bwd_noalloc_max_bytes": (c_size_t, []),
     "ts2ts_attn_bwd_noalloc": (c_int, [c_void_p] * 6 + [POINTER(c_int64)] * 5 + [c_int] * 4 + [c_float] + [c_void_p] * 4 + [c_int] * 2
                                + [c_void_p, c_size_t] + [c_void_p] * 3 + [POINTER(c_int64)] * 3 + [c_void_p]),
+    "ts2ts_detect_links_scratch_bytes": (c_size_t, [c_int]),
+    "ts2ts_detect_links": (c_int, [c_void_p, c_int, c_int, c_int64, POINTER(c_int64), c_int, c_void_p, c_int, c_int, c_int,
+                                   c_void_p, c_size_t, c_void_p, c_int, c_void_p, c_void_p]),
     "ts2ts_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int32)]),
     "ts2ts_profile_enable": (c_int, [c_int]),
     "ts2ts_profile_last_ms": (c_int, [c_int, POINTER(c_float)]),

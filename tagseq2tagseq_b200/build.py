@@ -16,7 +16,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libts2ts_attn.so")
-SOURCES = ["api.cu", "block_map.cu", "attn_fwd.cu", "attn_bwd.cu"]
+SOURCES = ["api.cu", "block_map.cu", "link_scan.cu", "attn_fwd.cu", "attn_bwd.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v"]
 

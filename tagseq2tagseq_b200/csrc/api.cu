@@ -6,6 +6,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include "link_scan.h"
 #include "plan.h"
 #include "profile.h"
 
@@ -22,6 +23,7 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
                PlanView P, MaskArgs M, void* dq, void* dk, void* dv, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv,
                void* workspace, cudaStream_t stream);
 int bwd_static_scratch(void** ptr, size_t* bytes);
+
 }  // namespace ts2ts
 
 namespace ts2ts {
@@ -196,6 +198,33 @@ int ts2ts_attn_bwd_noalloc(const void* q, const void* k, const void* v, const vo
   return ts2ts_attn_bwd(q, k, v, out, dout, lse, q_strides, k_strides, v_strides, out_strides, dout_strides, B, H, T, D, scale,
                         doc_ids, q_row_ids, kv_col_ids, link_bits, R, W, plan, plan_bytes, dq, dk, dv, dq_strides, dk_strides,
                         dv_strides, scratch, scratch_bytes, stream);
+}
+
+size_t ts2ts_detect_links_scratch_bytes(int T) {
+  if (T <= 0 || T > kMaxT) return 0;
+  return (static_cast<size_t>(T) * 2 * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
+}
+
+int ts2ts_detect_links(const void* tokens, int token_bytes, int T, int64_t mid_id, const int64_t* start_ids, int n_start,
+                       const uint8_t* close_flags, int vocab, int back_limit, int window, void* scratch, size_t scratch_bytes,
+                       int32_t* links, int max_links, int32_t* count, void* stream) {
+  if (T <= 0 || T > kMaxT) return fail(-1, "T must be in 1..%d (got %d)", kMaxT, T);
+  if (token_bytes != 4 && token_bytes != 8) return fail(-2, "token_bytes must be 4 or 8 (got %d)", token_bytes);
+  if (tokens == nullptr || !aligned(tokens, (size_t)token_bytes)) return fail(-3, "tokens: null or misaligned pointer");
+  if (start_ids == nullptr || n_start <= 0 || n_start > kMaxStartIds)
+    return fail(-6, "between 1 and %d start ids are needed (got %d)", kMaxStartIds, n_start);
+  if (close_flags == nullptr || vocab <= 0) return fail(-6, "close_flags is null or vocab=%d is not positive", vocab);
+  if (back_limit < 0 || window < 0) return fail(-6, "back_limit and window must not be negative");
+  if (scratch == nullptr || !aligned(scratch, 16) || scratch_bytes < ts2ts_detect_links_scratch_bytes(T))
+    return fail(-9, "scratch must be 16-byte aligned and hold %zu bytes", ts2ts_detect_links_scratch_bytes(T));
+  if (links == nullptr || count == nullptr || max_links <= 0) return fail(-3, "links / count: null pointer or max_links <= 0");
+  LinkScanArgs a;
+  a.tokens = tokens; a.token_bytes = token_bytes; a.T = T; a.mid_id = mid_id; a.n_start = n_start;
+  for (int i = 0; i < kMaxStartIds; ++i) a.start_ids[i] = i < n_start ? start_ids[i] : 0;
+  a.close_flags = close_flags; a.vocab = vocab; a.back_limit = back_limit; a.window = window;
+  cudaError_t e = launch_link_scan(a, static_cast<int32_t*>(scratch), links, max_links, count, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(-50, "link scan launch failed: %s", cudaGetErrorString(e));
+  return 0;
 }
 
 int ts2ts_read_status(const void* plan, void* stream, int32_t* status_out) {

@@ -253,15 +253,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tmem_ld_wait();
         if (is_full) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx8[i & 7] = fmaxf(mx8[i & 7], __uint_as_float(r[i]));
+          for (int i = 0; i < 16; ++i) mx8[i & 7] = fmax3(mx8[i & 7], __uint_as_float(r[i]), __uint_as_float(r[i + 16]));
         } else {
           const uint32_t bw = c == 0 ? bw0 : bw1;
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            mx8[i & 7] = fmaxf(mx8[i & 7], ((bw >> i) & 1u) ? __uint_as_float(r[i]) : -CUDART_INF_F);
+          for (int i = 0; i < 16; ++i)
+            mx8[i & 7] = fmax3(mx8[i & 7], ((bw >> i) & 1u) ? __uint_as_float(r[i]) : -CUDART_INF_F,
+                               ((bw >> (i + 16)) & 1u) ? __uint_as_float(r[i + 16]) : -CUDART_INF_F);
         }
       }
-      float mx = fmaxf(fmaxf(fmaxf(mx8[0], mx8[1]), fmaxf(mx8[2], mx8[3])), fmaxf(fmaxf(mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7])));
+      float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
       s_mx[j & 1][half][row] = mx;
       mbar_arrive(&bar_mx[warp & 3]);
       if (!(ok = mbar_wait(&bar_mx[warp & 3], j & 1, &abort_word, 34))) break;

@@ -40,3 +40,25 @@ def test_size_queries_and_argument_rejection_need_no_gpu():
     assert L.ts2ts_attn_fwd(16, 16, 16, s3, s3, s3, 1, 1, 128, 96, 0.1, 16, None, None, None, 0, 0, 256, 1 << 20, 16, s3, 16, None) == -2
     bad = (ctypes.c_int64 * 3)(128, 128, 3)
     assert L.ts2ts_attn_fwd(16, 16, 16, bad, s3, s3, 1, 1, 128, 128, 0.1, 16, None, None, None, 0, 0, 256, 1 << 20, 16, s3, 16, None) == -5
+
+
+def test_link_scan_argument_rejection_needs_no_gpu():
+    L = _lib.lib()
+    assert L.ts2ts_detect_links_scratch_bytes(0) == 0
+    assert L.ts2ts_detect_links_scratch_bytes(1000) >= 8000
+    starts = (ctypes.c_int64 * 2)(58, 685)
+    ok_args = dict(tokens=16, tb=8, T=128, mid=16151, starts=starts, ns=2, flags=16, vocab=50257, back=100, win=50, scratch=16,
+                   sbytes=1 << 20, links=16, maxl=8, count=16)
+
+    def call(**kw):
+        a = {**ok_args, **kw}
+        return L.ts2ts_detect_links(a["tokens"], a["tb"], a["T"], a["mid"], a["starts"], a["ns"], a["flags"], a["vocab"], a["back"],
+                                    a["win"], a["scratch"], a["sbytes"], a["links"], a["maxl"], a["count"], None)
+
+    assert call(T=0) == -1
+    assert call(tb=2) == -2
+    assert call(tokens=None) == -3
+    assert call(ns=0) == -6 and call(ns=9) == -6
+    assert call(flags=None) == -6 and call(win=-1) == -6
+    assert call(sbytes=16) == -9
+    assert call(links=None) == -3
