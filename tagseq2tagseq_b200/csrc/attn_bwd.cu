@@ -5,17 +5,19 @@
 //   attn_bwd     one CTA per 128-key tile of one (batch, head); walks the non-skipped 128-query tiles of the
 //                transposed block list.  Everything is transposed so that a tensor-memory lane is a key row:
 //                  tcgen05  S^T = K Q^T,  dP^T = V dO^T            [128 keys x 128 queries, fp32 in TMEM, N = 128]
-//                  warps 0-7 (two threads per key row), in two halves of 64 queries:
-//                           P^T = exp2(scale S^T - lse2[q]) under the mask, dS^T = P^T (dP^T - delta[q]);
-//                           both written as bf16 over the S^T columns just read, dS^T also to shared memory
+//                  warps 0-7 (two threads per key row, 64 queries each), in two phases:
+//                           P^T = exp2(scale S^T - lse2[q]) under the mask, as soon as S^T is complete, written as
+//                           bf16 over the S^T columns just read; then, once dP^T is complete and in two halves of 64
+//                           queries, dS^T = P^T (dP^T - delta[q]) as bf16 next to P^T and to shared memory
 //                  tcgen05  dV += P^T dO,  dK += dS^T Q           (A from TMEM, B MN-major from smem; issued per
-//                           half, so the first half's MMAs overlap the second half's exponentials)
+//                           half, so the first half's MMAs overlap the second half's dS^T arithmetic)
+//                           S^T of the NEXT tile, so that its exponentials run under the MMAs that follow
 //                           dQ^T = K^T dS^T                       [D x 128 queries over the consumed dP^T columns]
-//                  warps 8-11 (thread = head-dim lane)  dQ^T -> scaled fp32 tile in the just-consumed Q / dO stage of
-//                           shared memory (one 32-lane box per warp) -> one TMA reduce-add per warp into the dQ
-//                           accumulator, while the tensor core already computes the next tile's S^T
-//                Q / dO tiles are double-buffered in shared memory.  dK (scaled) and dV leave through shared
-//                memory and TMA stores at the end.
+//                           dP^T of the next tile once dQ^T has been read out
+//                  warps 8-11 (thread = head-dim lane)  dQ^T -> scaled fp32, 32 queries at a time, through two
+//                           private shared-memory boxes per warp -> TMA reduce-adds into the dQ accumulator
+//                Q tiles are double-buffered in shared memory, dO has one buffer that is reloaded between the dV MMAs of
+//                a tile and dP^T of the next.  dK (scaled) and dV leave through shared memory and TMA stores at the end.
 //   dq_convert   dQ accumulator (fp32, already scaled) -> bf16 dq
 //
 // Computes what the reference gets from autograd of PyTorch FlexAttention
@@ -67,10 +69,11 @@ struct BwdSmem {
   static constexpr int kSub = D / 64;
   static constexpr int kTileBytes = kTile * D * 2;
   static constexpr int kDsBytes = kTile * kTile * 2;  // dS^T: two halves of [128 key rows x 128 B]
-  // K, V, two (Q, dO) stages, dS^T, then row statistics, barriers and flags; plus alignment slack.
-  // The kernel declares no static shared memory, so the dynamic region normally starts 1024-byte aligned and the
-  // slack stays unused; if it ever does not fit, the kernel reports status 2900 instead of running.
-  static constexpr int kTiles = 6 * kTileBytes + kDsBytes;
+  static constexpr int kStageBytes = 4 * 2 * 4096;     // dQ staging: per reduction warp two boxes of [32 queries x 32 floats]
+  // K, V, two Q stages, one dO buffer, dS^T, the dQ staging boxes, then row statistics, barriers and flags; plus
+  // alignment slack.  The kernel declares no static shared memory, so the dynamic region normally starts 1024-byte
+  // aligned and the slack stays unused; if it ever does not fit, the kernel reports status 2900 instead of running.
+  static constexpr int kTiles = 5 * kTileBytes + kDsBytes + kStageBytes;
   static constexpr int kSmall = 4 * kTile * 4 + 16 * 8 + 16;
   static constexpr int kSlack = 512;
   static constexpr int kBytes = kTiles + kSmall + kSlack;
@@ -107,14 +110,17 @@ __device__ __forceinline__ void allowed_rows(const PlanView& P, const MaskArgs& 
   }
 }
 
-// One 32-column chunk of a sub-step: P^T and dS^T (packed bf16 pairs) from S^T, dP^T, the row statistics of the 32
-// queries (read from shared memory; every lane of a warp reads the same addresses) and the mask.
-__device__ __forceinline__ void pds_chunk(const uint32_t (&s)[32], const uint32_t (&dp)[32], const float* l2, const float* dl,
-                                          uint32_t bw, bool masked, float scale_log2, uint32_t* pk, uint32_t* dsk) {
+// The per-tile arithmetic of a compute thread, 32 query columns at a time, in two phases so that the first can run
+// while the tensor core still works on dQ^T of the previous tile and dP^T of this one:
+//   p_chunk   P^T = exp2(scale S^T - lse2) under the mask, packed to bf16 pairs (the MMA operand, also kept in
+//             registers for the second phase)
+//   ds_chunk  dS^T = P^T (dP^T - delta), from the bf16 P^T, packed to bf16 pairs
+// The row statistics of the 32 queries are read from shared memory; every lane of a warp reads the same addresses.
+__device__ __forceinline__ void p_chunk(const uint32_t (&s)[32], const float* l2, uint32_t bw, bool masked, float scale_log2,
+                                        uint32_t (&pk)[16]) {
 #pragma unroll
   for (int e = 0; e < 32; e += 4) {
     const float4 l4 = *reinterpret_cast<const float4*>(l2 + e);
-    const float4 d4 = *reinterpret_cast<const float4*>(dl + e);
     float p0 = fast_exp2(fmaf(__uint_as_float(s[e + 0]), scale_log2, -l4.x));
     float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), scale_log2, -l4.y));
     float p2 = fast_exp2(fmaf(__uint_as_float(s[e + 2]), scale_log2, -l4.z));
@@ -127,6 +133,15 @@ __device__ __forceinline__ void pds_chunk(const uint32_t (&s)[32], const uint32_
     }
     pk[(e >> 1) + 0] = pack_bf16(p0, p1);
     pk[(e >> 1) + 1] = pack_bf16(p2, p3);
+  }
+}
+__device__ __forceinline__ void ds_chunk(const uint32_t (&pk)[16], const uint32_t (&dp)[32], const float* dl, uint32_t (&dsk)[16]) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+    const float4 d4 = *reinterpret_cast<const float4*>(dl + e);
+    const uint32_t a = pk[(e >> 1) + 0], c = pk[(e >> 1) + 1];
+    const float p0 = __uint_as_float(a << 16), p1 = __uint_as_float(a & 0xffff0000u);
+    const float p2 = __uint_as_float(c << 16), p3 = __uint_as_float(c & 0xffff0000u);
     dsk[(e >> 1) + 0] = pack_bf16(p0 * (__uint_as_float(dp[e + 0]) - d4.x), p1 * (__uint_as_float(dp[e + 1]) - d4.y));
     dsk[(e >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dp[e + 2]) - d4.z), p3 * (__uint_as_float(dp[e + 3]) - d4.w));
   }
@@ -146,19 +161,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint8_t* sK = smem;
   uint8_t* sV = smem + Cfg::kTileBytes;           // must follow sK directly (dQ^T operand padding for D = 64)
   uint8_t* sQ = smem + 2 * Cfg::kTileBytes;       // two stages, Cfg::kTileBytes each
-  uint8_t* sDO = smem + 4 * Cfg::kTileBytes;      // two stages
-  uint8_t* sDS = smem + 6 * Cfg::kTileBytes;      // dS^T, halves of 16 KB
+  uint8_t* sDO = smem + 4 * Cfg::kTileBytes;      // one buffer: reloaded between the dV MMAs of a tile and dP^T of the next
+  uint8_t* sDS = smem + 5 * Cfg::kTileBytes;      // dS^T, halves of 16 KB
+  uint8_t* sStage = sDS + Cfg::kDsBytes;          // dQ staging boxes
   float (*s_lse2)[kTile] = reinterpret_cast<float (*)[kTile]>(smem + Cfg::kTiles);
   float (*s_delta)[kTile] = reinterpret_cast<float (*)[kTile]>(smem + Cfg::kTiles + 2 * kTile * 4);
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::kTiles + 4 * kTile * 4);
   uint64_t& bar_kv = bars[0];
-  uint64_t* bar_qdo_full = bars + 1;   // [2] Q, dO, lse2, delta of a stage landed
-  uint64_t* bar_qdo_free = bars + 3;   // [2] stage reusable: its MMAs completed and the dQ tile staged in it was read by TMA
+  uint64_t* bar_q_full = bars + 1;     // [2] Q, lse2, delta of a stage landed
+  uint64_t& bar_do_full = bars[3];     // dO of the tile landed
+  uint64_t& bar_gd = bars[4];          // dV / dK MMAs of the tile completed: its Q stage and the dO buffer may be reloaded
   uint64_t& bar_st = bars[5];          // S^T and dP^T of the tile are in tensor memory
   uint64_t* bar_pds = bars + 6;        // [2] P^T / dS^T of a 64-query half written
   uint64_t& bar_g = bars[8];           // gradient MMAs of the tile completed (dQ^T readable)
   uint64_t& bar_dqr = bars[9];         // dQ^T read out of tensor memory
   uint64_t& bar_epi = bars[10];
+  uint64_t& bar_s = bars[12];          // S^T of the tile is in tensor memory (dP^T may still be running)
   uint64_t& bar_issued = bars[11];     // S^T and dP^T MMAs of the tile handed to the tensor pipe
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_ptr = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars + 16) + 4);
@@ -197,15 +215,17 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     *abort_ptr = 0;
     mbar_init(&bar_kv, 1);
     for (int i = 0; i < 2; ++i) {
-      mbar_init(&bar_qdo_full[i], 1);
-      mbar_init(&bar_qdo_free[i], D / 32);
+      mbar_init(&bar_q_full[i], 1);
       mbar_init(&bar_pds[i], 2 * kTile);
     }
+    mbar_init(&bar_do_full, 1);
+    mbar_init(&bar_gd, 1);
     mbar_init(&bar_st, 1);
     mbar_init(&bar_g, 1);
     mbar_init(&bar_dqr, kTile);
     mbar_init(&bar_epi, 2 * kTile);
     mbar_init(&bar_issued, 1);
+    mbar_init(&bar_s, 1);
     fence_mbar_init();
   }
   __syncthreads();
@@ -231,18 +251,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tma_load_4d(sK + s * 16384, &mapK, &bar_kv, s * 64, kb * kTile, h, b);
         tma_load_4d(sV + s * 16384, &mapV, &bar_kv, s * 64, kb * kTile, h, b);
       }
-      for (int i = 0; i < n; ++i) {
+      auto load_q = [&](int i) {  // Q tile and row statistics of tile i into stage i & 1
         const int qb = list[i] & ~kFullBit;
         const int st = i & 1;
-        if (i >= 2 && !mbar_wait(&bar_qdo_free[st], ((i - 2) >> 1) & 1, abort_w, 11)) break;
-        mbar_expect_tx(&bar_qdo_full[st], 2 * Cfg::kTileBytes + 2 * kTile * 4);
-        for (int s = 0; s < Cfg::kSub; ++s) {
-          tma_load_4d(sQ + st * Cfg::kTileBytes + s * 16384, &mapQ, &bar_qdo_full[st], s * 64, qb * kTile, h, b);
-          tma_load_4d(sDO + st * Cfg::kTileBytes + s * 16384, &mapDO, &bar_qdo_full[st], s * 64, qb * kTile, h, b);
-        }
+        mbar_expect_tx(&bar_q_full[st], Cfg::kTileBytes + 2 * kTile * 4);
+        for (int s = 0; s < Cfg::kSub; ++s)
+          tma_load_4d(sQ + st * Cfg::kTileBytes + s * 16384, &mapQ, &bar_q_full[st], s * 64, qb * kTile, h, b);
         const size_t stat = ((size_t)b * p.H + h) * p.Tp + (size_t)qb * kTile;
-        bulk_load(s_lse2[st], p.lse2 + stat, kTile * 4, &bar_qdo_full[st]);
-        bulk_load(s_delta[st], p.delta + stat, kTile * 4, &bar_qdo_full[st]);
+        bulk_load(s_lse2[st], p.lse2 + stat, kTile * 4, &bar_q_full[st]);
+        bulk_load(s_delta[st], p.delta + stat, kTile * 4, &bar_q_full[st]);
+      };
+      auto load_do = [&](int i) {
+        const int qb = list[i] & ~kFullBit;
+        mbar_expect_tx(&bar_do_full, Cfg::kTileBytes);
+        for (int s = 0; s < Cfg::kSub; ++s) tma_load_4d(sDO + s * 16384, &mapDO, &bar_do_full, s * 64, qb * kTile, h, b);
+      };
+      load_q(0);
+      load_do(0);
+      if (n > 1) load_q(1);
+      for (int i = 0; i + 1 < n; ++i) {
+        if (!mbar_wait(&bar_gd, i & 1, abort_w, 11)) break;  // dV / dK MMAs of tile i done: dO and Q stage i & 1 are free
+        load_do(i + 1);
+        if (i + 2 < n) load_q(i + 2);
       }
     } else if (warp == 13 && lane == 0) {
       // ---------------------------------------------------------------- MMA issuer
@@ -259,70 +289,88 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       // Shared-memory accesses of this thread (barrier waits included) queue behind the MMAs it has issued and only
       // proceed once the tensor pipe has accepted those, so every wait whose barrier is normally complete already
       // is placed one or two MMAs before the end of a group: the pipe stays fed while the wait runs.
-      constexpr int kStLast = D / 16 - 1;
-      auto issue_st = [&](uint32_t stage, int kk) {
-        const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
-        mma_ss2(tST, k_kmaj + off, hi, q_kmaj + stage + off, hi, idesc_st, kk > 0);
+      auto issue_st = [&](uint32_t stage) {  // S^T = K Q^T, then tell the compute warps
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
+          mma_ss2(tST, k_kmaj + off, hi, q_kmaj + stage + off, hi, idesc_st, kk > 0);
+        }
+        mma_commit(&bar_s);
       };
-      bool ok = mbar_wait(&bar_kv, 0, abort_w, 21) && mbar_wait(&bar_qdo_full[0], 0, abort_w, 22);
+      auto issue_dpt = [&]() {  // dP^T = V dO^T
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
+          mma_ss2(tDPT, v_kmaj + off, hi, do_kmaj + off, hi, idesc_st, kk > 0);
+        }
+        mma_commit(&bar_st);
+        mbar_arrive(&bar_issued);
+      };
+      auto issue_dqt = [&]() {  // dQ^T = K^T dS^T   (K = 128 keys; M = D, padded to 128 lanes when D = 64)
+#pragma unroll
+        for (int kk = 0; kk < kTile / 16; ++kk) mma_ss2(tDPT, k_mn + kk * 128, hi, ds_mn + kk * 128, hi, idesc_dq, kk > 0);
+        mma_commit(&bar_g);
+      };
+      // Order per tile i: dV/dK(i) half 0, half 1 | S^T(i+1) | dQ^T(i) | (dQ^T(i) read out) dP^T(i+1).
+      // S^T of the next tile goes first so that the compute warps can do the exponentials of tile i+1 while the
+      // tensor core is busy with dQ^T(i), its read-out and dP^T(i+1).  S^T(i+1) overwrites the P^T / dS^T columns of
+      // tile i; their readers, the dV / dK MMAs of tile i, were issued before it by this thread and the tensor pipe
+      // executes one thread's MMAs in issue order.
+      bool ok = mbar_wait(&bar_kv, 0, abort_w, 21) && mbar_wait(&bar_q_full[0], 0, abort_w, 22);
       if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int kk = 0; kk < kStLast; ++kk) issue_st(0u, kk);
+        issue_st(0u);
+        ok = mbar_wait(&bar_do_full, 0, abort_w, 27);
+        if (ok) issue_dpt();
       }
       for (int i = 0; i < n && ok; ++i) {
         const int st = i & 1;
         const uint32_t stage = ((uint32_t)st * Cfg::kTileBytes) >> 4;
-        // S^T of this tile is issued except for its last MMA.  It may run while dQ^T of the previous tile is still
-        // being read: it only overwrites the P^T / dS^T columns, whose readers (the dV / dK MMAs of the previous
-        // tile) were issued before the previous dQ^T MMAs.
-        TRACE(0, i, 0);
-        if (i > 0 && !mbar_wait(&bar_dqr, (i - 1) & 1, abort_w, 23)) break;  // dQ^T of the previous tile read out
-        tc_fence_after();
-        issue_st(stage, kStLast);
-        TRACE(0, i, 1);
-#pragma unroll
-        for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
-          mma_ss2(tDPT, v_kmaj + off, hi, do_kmaj + stage + off, hi, idesc_st, kk > 0);
-        }
-        mma_commit(&bar_st);
-        mbar_arrive(&bar_issued);
-        TRACE(0, i, 2);
+        const uint32_t next = ((uint32_t)(st ^ 1) * Cfg::kTileBytes) >> 4;
+        const bool more = i + 1 < n;
         bool fail = false;
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
           if (!mbar_wait(&bar_pds[s], i & 1, abort_w, 24)) { fail = true; break; }
           tc_fence_after();
           TRACE(0, i, 3 + s);
-          const uint32_t rows = stage + ((uint32_t)s * (kSubQ * 128) >> 4);  // 64 query rows x 128 B into the stage
+          const uint32_t half_rows = (uint32_t)s * (kSubQ * 128) >> 4;  // 64 query rows x 128 B
           const uint32_t acc = (i > 0 || s > 0) ? 1u : 0u;
 #pragma unroll
           for (int kk = 0; kk < kSubQ / 16; ++kk)  // dV += P^T dO   (K = 64 queries of this half)
-            mma_ts2(tDV, tST + 64 * s + (kk >> 1) * 32 + (kk & 1) * 8, do_mn + rows + kk * 128, hi, idesc_g, kk > 0 ? 1u : acc);
+            mma_ts2(tDV, tST + 64 * s + (kk >> 1) * 32 + (kk & 1) * 8, do_mn + half_rows + kk * 128, hi, idesc_g, kk > 0 ? 1u : acc);
 #pragma unroll
           for (int kk = 0; kk < kSubQ / 16; ++kk)  // dK += dS^T Q
-            mma_ts2(tDK, tST + 64 * s + (kk >> 1) * 32 + 16 + (kk & 1) * 8, q_mn + rows + kk * 128, hi, idesc_g, kk > 0 ? 1u : acc);
+            mma_ts2(tDK, tST + 64 * s + (kk >> 1) * 32 + 16 + (kk & 1) * 8, q_mn + stage + half_rows + kk * 128, hi, idesc_g, kk > 0 ? 1u : acc);
         }
         if (fail) break;
-        // dQ^T = K^T dS^T   (K = 128 keys; M = D, padded to 128 lanes when D = 64)
-        constexpr int kDqSplit = kTile / 16 - 2;
-#pragma unroll
-        for (int kk = 0; kk < kDqSplit; ++kk) mma_ss2(tDPT, k_mn + kk * 128, hi, ds_mn + kk * 128, hi, idesc_dq, kk > 0);
-        const bool more = i + 1 < n;
-        if (more && !mbar_wait(&bar_qdo_full[st ^ 1], ((i + 1) >> 1) & 1, abort_w, 22)) break;
-#pragma unroll
-        for (int kk = kDqSplit; kk < kTile / 16; ++kk) mma_ss2(tDPT, k_mn + kk * 128, hi, ds_mn + kk * 128, hi, idesc_dq, 1u);
-        mma_commit(&bar_g);
+        mma_commit(&bar_gd);
+#ifdef TS2TS_STRICT_ORDER
+        issue_dqt();
         TRACE(0, i, 5);
         if (more) {
-#ifdef TS2TS_STRICT_ORDER
-          if (!mbar_wait(&bar_g, i & 1, abort_w, 26)) break;
-#endif
+          if (!mbar_wait(&bar_q_full[st ^ 1], ((i + 1) >> 1) & 1, abort_w, 22)) break;
+          if (!mbar_wait(&bar_g, i & 1, abort_w, 26)) break;  // every MMA of tile i complete before S^T(i+1) is issued
           tc_fence_after();
-          const uint32_t next = ((uint32_t)(st ^ 1) * Cfg::kTileBytes) >> 4;
-#pragma unroll
-          for (int kk = 0; kk < kStLast; ++kk) issue_st(next, kk);
+          issue_st(next);
+        }
+#else
+        if (more) {
+          if (!mbar_wait(&bar_q_full[st ^ 1], ((i + 1) >> 1) & 1, abort_w, 22)) break;
+          tc_fence_after();
+          issue_st(next);
+          TRACE(0, i, 0);
+        }
+        issue_dqt();
+        TRACE(0, i, 5);
+#endif
+        if (more) {
+          if (!mbar_wait(&bar_dqr, i & 1, abort_w, 23)) break;  // dQ^T(i) read out of the columns dP^T(i+1) overwrites
+          if (!mbar_wait(&bar_do_full, (i + 1) & 1, abort_w, 27)) break;
+          tc_fence_after();
+          TRACE(0, i, 1);
+          issue_dpt();
+          TRACE(0, i, 2);
         }
       }
     }
@@ -353,22 +401,36 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           }
         }
       }
-      if (!(ok = mbar_wait(&bar_qdo_full[st], (i >> 1) & 1, abort_w, 30))) break;  // lse2 / delta of this tile landed
+      if (!(ok = mbar_wait(&bar_q_full[st], (i >> 1) & 1, abort_w, 30))) break;  // lse2 / delta of this tile landed
+      // ---- phase 1: exponentials, as soon as S^T is complete
+      if (!(ok = mbar_wait(&bar_s, i & 1, abort_w, 35))) break;
+      tc_fence_after();
+      if (tid == 0) TRACE(1, i, 0);
+      uint32_t pk[2][16];
 #pragma unroll
       for (int s = 0; s < 2; ++s) {
-        if (s == 0 && !(ok = mbar_wait(&bar_st, i & 1, abort_w, 31))) break;
-        tc_fence_after();
-        if (tid == 0) TRACE(1, i, 4 * s + 0);
         const uint32_t col = lane_base + 64 * s + 32 * half;
-        uint32_t sv[32], dp[32], pk[16], dsk[16];
+        const uint32_t bw = s == 0 ? (half == 0 ? bits[0] : bits[1]) : (half == 0 ? bits[2] : bits[3]);
+        uint32_t sv[32];
         tmem_ld32(tST + col, sv);
+        tmem_ld_wait();
+        if (tid == 0) TRACE(1, i, s == 0 ? 4 : 6);
+        p_chunk(sv, s_lse2[st] + s * kSubQ + 32 * half, bw, masked, p.scale_log2, pk[s]);
+        if (tid == 0 && s == 0) TRACE(1, i, 5);
+        tmem_st16(tST + col, pk[s]);
+      }
+      if (tid == 0) TRACE(1, i, 1);
+      // ---- phase 2: dS^T, once dP^T is complete
+      if (!(ok = mbar_wait(&bar_st, i & 1, abort_w, 31))) break;
+      tc_fence_after();
+      if (tid == 0) TRACE(1, i, 2);
+#pragma unroll
+      for (int s = 0; s < 2; ++s) {
+        const uint32_t col = lane_base + 64 * s + 32 * half;
+        uint32_t dp[32], dsk[16];
         tmem_ld32(tDPT + col, dp);
         tmem_ld_wait();
-        if (tid == 0) TRACE(1, i, 4 * s + 1);
-        const uint32_t bw = s == 0 ? (half == 0 ? bits[0] : bits[1]) : (half == 0 ? bits[2] : bits[3]);
-        pds_chunk(sv, dp, s_lse2[st] + s * kSubQ + 32 * half, s_delta[st] + s * kSubQ + 32 * half, bw, masked, p.scale_log2, pk, dsk);
-        if (tid == 0) TRACE(1, i, 4 * s + 2);
-        tmem_st16(tST + col, pk);
+        ds_chunk(pk[s], dp, s_delta[st] + s * kSubQ + 32 * half, dsk);
         tmem_st16(tST + col + 16, dsk);
         // dS^T row `row`, queries [64 s + 32 half, +32): four 16-byte chunks of the 128-byte row of half s
         uint8_t* ds_row = sDS + s * 16384;
@@ -379,19 +441,20 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         fence_async_smem();
         tc_fence_before();
         mbar_arrive(&bar_pds[s]);
-        if (tid == 0) TRACE(1, i, 4 * s + 3);
+        if (tid == 0) TRACE(1, i, 3 + 4 * s);
       }
     }
-    // ---- epilogue: dV (query-half 0 threads) and scale * dK (half 1) -> bf16 -> swizzled smem (stage 0 of Q / dO is
-    //      free) -> TMA stores
-    //      The stage not used by the last tile is free once the dQ tile of tile n-2 has been read out of it.
+    // ---- epilogue: dV (query-half 0 threads) and scale * dK (half 1) -> bf16 -> swizzled smem -> TMA stores.
+    //      dV goes through the Q stage the last tile did not use, dK through the dO buffer (its last readers, the
+    //      dV MMAs of the last tile, completed before bar_g).
     const int est = n & 1;
     if (ok) ok = mbar_wait(&bar_g, (n - 1) & 1, abort_w, 32);
-    if (ok && n >= 2) ok = mbar_wait(&bar_qdo_free[est], ((n - 2) >> 1) & 1, abort_w, 34);
     tc_fence_after();
+    uint8_t* out_dv = sQ + est * Cfg::kTileBytes;
+    uint8_t* out_dk = sDO;
     if (ok) {
       const uint32_t tsrc = half == 0 ? tDV : tDK;
-      uint8_t* stage = (half == 0 ? sQ : sDO) + est * Cfg::kTileBytes;
+      uint8_t* stage = half == 0 ? out_dv : out_dk;
       const float f = half == 0 ? 1.f : p.scale;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
@@ -414,8 +477,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
     if (tid == 0 && ok && mbar_wait(&bar_epi, 0, abort_w, 33)) {
       for (int s = 0; s < Cfg::kSub; ++s) {
-        tma_store_4d(&mapDV, sQ + est * Cfg::kTileBytes + s * 16384, s * 64, kb * kTile, h, b);
-        tma_store_4d(&mapDK, sDO + est * Cfg::kTileBytes + s * 16384, s * 64, kb * kTile, h, b);
+        tma_store_4d(&mapDV, out_dv + s * 16384, s * 64, kb * kTile, h, b);
+        tma_store_4d(&mapDK, out_dk + s * 16384, s * 64, kb * kTile, h, b);
       }
       tma_store_commit();
       tma_store_wait_all();
@@ -425,51 +488,53 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     reg_inc<168>();
     const int dlane = tid - 2 * kTile;  // 0..127 = TMEM lane = index into D
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    // Each warp owns one 128-byte-swizzled fp32 box of [128 queries x 32 floats]: box d/32 lives in the Q stage
-    // (first D/64 boxes) or the dO stage (the rest).  The warp stages its box and reduces it with its own TMA request.
+    // Each warp owns the 32 head-dim lanes d/32 of the dQ tile and two private 128-byte-swizzled fp32 boxes of
+    // [32 queries x 32 floats] in shared memory.  The tile leaves in four rounds of 32 queries: store a round into
+    // one box, hand it to a TMA reduce-add, and store the next round into the other box while the first is read.
+    // Nothing else in the CTA waits for these reads.
     const int box = dlane >> 5, chunk = (dlane & 31) >> 2, word = dlane & 3;
     const bool has_box = box * 32 < D;
+    uint8_t* my_stage = sStage + (warp & 3) * 8192;
     // The warp on the MMA issuer's scheduler partition shares that partition's memory-instruction queue with it:
-    // its 128 stores would be interleaved with the S^T / dP^T MMAs of the next tile and double their issue time.
-    // It holds its values in registers until those MMAs have been handed over.
+    // its stores would be interleaved with the S^T / dP^T MMAs of the next tile and slow their issue.  It holds its
+    // values in registers until dP^T of the next tile has been handed over.
     const bool behind_issuer = (warp & 3) == (13 & 3);
     bool ok = true;
     for (int i = 0; i < n; ++i) {
       const int qb = list[i] & ~kFullBit;
-      const int st = i & 1;
       if (!(ok = mbar_wait(&bar_g, i & 1, abort_w, 41))) break;
       tc_fence_after();
       if (tid == 2 * kTile) TRACE(2, i, 0);
-      uint32_t r0[32], r1[32], r2[32], r3[32];
-      tmem_ld32(tDPT + lane_base, r0);
-      tmem_ld32(tDPT + lane_base + 32, r1);
-      tmem_ld32(tDPT + lane_base + 64, r2);
-      tmem_ld32(tDPT + lane_base + 96, r3);
+      uint32_t r[4][32];
+      tmem_ld32(tDPT + lane_base, r[0]);
+      tmem_ld32(tDPT + lane_base + 32, r[1]);
+      tmem_ld32(tDPT + lane_base + 64, r[2]);
+      tmem_ld32(tDPT + lane_base + 96, r[3]);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&bar_dqr);  // the dP^T / dQ^T columns may be overwritten from here on
+      mbar_arrive(&bar_dqr);  // the dP^T / dQ^T columns may be overwritten once all four warps have arrived
       if (tid == 2 * kTile) TRACE(2, i, 1);
       if (!has_box) continue;
       if (behind_issuer && i + 1 < n && !(ok = mbar_wait(&bar_issued, (i + 1) & 1, abort_w, 43))) break;
-      uint8_t* box_base = (box < Cfg::kSub ? sQ : sDO) + st * Cfg::kTileBytes + (box % Cfg::kSub) * 16384;
-      uint8_t* base = box_base + word * 4;
+      if (tid == 2 * kTile) TRACE(2, i, 3);
 #pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        *reinterpret_cast<float*>(base + (c) * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r0[c]) * p.scale;
-        *reinterpret_cast<float*>(base + (32 + c) * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r1[c]) * p.scale;
-        *reinterpret_cast<float*>(base + (64 + c) * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r2[c]) * p.scale;
-        *reinterpret_cast<float*>(base + (96 + c) * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r3[c]) * p.scale;
+      for (int k = 0; k < 4; ++k) {
+        uint8_t* buf = my_stage + (k & 1) * 4096;
+        // the box was last used two rounds ago: at most the previous round may still be reading
+        if (lane == 0) tma_store_wait_read1();
+        __syncwarp();
+        uint8_t* base = buf + word * 4;
+#pragma unroll
+        for (int c = 0; c < 32; ++c)
+          *reinterpret_cast<float*>(base + c * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r[k][c]) * p.scale;
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          tma_reduce_add_4d(&mapDQ, buf, box * 32, qb * kTile + 32 * k, h, b);
+          tma_store_commit();
+        }
       }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) {
-        tma_reduce_add_4d(&mapDQ, box_base, box * 32, qb * kTile, h, b);
-        tma_store_commit();
-        tma_store_wait_read();       // shared memory read; the global reduction may still be in flight
-        mbar_arrive(&bar_qdo_free[st]);
-        if (tid == 2 * kTile) TRACE(2, i, 2);
-      }
-      __syncwarp();
+      if (tid == 2 * kTile) TRACE(2, i, 4);
     }
     if (lane == 0 && has_box) tma_store_wait_all();
   }
@@ -560,7 +625,7 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   if ((r = make_tile_map(&mdo, dout, 2, B, H, T, D, sdo[0], sdo[1], sdo[2], kTile, 64))) return r;
   if ((r = make_tile_map(&mdk, dk, 2, B, H, T, D, sdk[0], sdk[1], sdk[2], kTile, 64))) return r;
   if ((r = make_tile_map(&mdv, dv, 2, B, H, T, D, sdv[0], sdv[1], sdv[2], kTile, 64))) return r;
-  if ((r = make_tile_map(&mdq, dq_acc, 4, B, H, Tp, D, (int64_t)H * Tp * D, (int64_t)Tp * D, D, kTile, 32))) return r;
+  if ((r = make_tile_map(&mdq, dq_acc, 4, B, H, Tp, D, (int64_t)H * Tp * D, (int64_t)Tp * D, D, 32, 32))) return r;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);

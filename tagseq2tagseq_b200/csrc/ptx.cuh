@@ -98,6 +98,8 @@ __device__ __forceinline__ void tma_reduce_add_4d(const void* tmap, const void* 
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// At most one of this thread's bulk groups may still be reading its shared-memory source afterwards.
+__device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
 // ----------------------------------------------------------------------------- TMEM
 // Allocation is warp-wide (.sync.aligned): one full warp calls these.
