@@ -4,16 +4,17 @@
 // non-skipped key tiles listed for it in the block plan.  Per key tile:
 //   TMA       K, V tiles -> shared memory (128-byte swizzle)
 //   tcgen05   S = Q K^T           (bf16 x bf16 -> fp32 in tensor memory)
-//   softmax   8 warps, two threads per query row (64 key columns each): tcgen05.ld S,
-//             mask (partial tiles only, by bit tests against a per-row 128-bit column
-//             mask built from the tile's runs), online softmax in base 2 (the two
-//             half-row maxima meet through shared memory), P -> bf16 -> tcgen05.st over
-//             the S columns the thread has just read
+//   softmax   4 warps, one thread per query row: tcgen05.ld of the row's 128 scores once into
+//             registers, mask (partial tiles only, by bit tests against a per-row 128-bit column
+//             mask built from the tile's runs), online softmax in base 2 (row maximum and sum
+//             need no exchange between threads), P -> bf16 -> tcgen05.st over the first 64
+//             score columns
 //   tcgen05   O += P V            (P read from tensor memory, V MN-major from smem)
 // The accumulator is rescaled lazily: only when a row's running maximum grows
 // by more than 2^8, so most tiles never touch O in the softmax warps.
 //
-// Roles: warps 0-7 softmax / epilogue, warp 8 TMA producer, warp 9 MMA issuer.
+// Roles: warps 0-3 softmax / epilogue (setmaxnreg 216), warp 4 TMA producer, warp 5 MMA
+// issuer (40 registers; warps 6-7 only complete the warpgroup for setmaxnreg).
 // Shared memory 3 tiles (Q, K, V) so two CTAs fit on one SM and overlap one
 // another's softmax and MMA phases; 256 TMEM columns per CTA (S/P 128, O <=128).
 //
@@ -55,7 +56,10 @@ struct FwdParams {
 #define FTRACE(role, step, ev) do { } while (0)
 #endif
 
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 256;  // warps 0-3 softmax (thread = query row), 4 TMA producer, 5 MMA issuer, 6-7 idle
+constexpr int kFwdProducerWarp = 4, kFwdMmaWarp = 5;
+template <uint32_t N> __device__ __forceinline__ void fwd_reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+template <uint32_t N> __device__ __forceinline__ void fwd_reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 constexpr float kRescaleThreshold = 8.0f;
 
 template <int D>
@@ -103,9 +107,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint8_t* sQ = smem;
   uint8_t* sK = smem + Cfg::kTileBytes;
   uint8_t* sV = smem + 2 * Cfg::kTileBytes;
-  __shared__ uint64_t bar_q, bar_k, bar_v, bar_s, bar_p, bar_o, bar_epi, bar_mx[4], bar_l;
-  __shared__ float s_mx[2][2][kTile];  // [tile parity][column half][row]: half-row maxima
-  __shared__ float s_l[2][kTile];      // [column half][row]: half-row sums, exchanged once at the end
+  __shared__ uint64_t bar_q, bar_k, bar_v, bar_s, bar_p, bar_o, bar_epi;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_word;
 
@@ -137,15 +139,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     mbar_init(&bar_k, 1);
     mbar_init(&bar_v, 1);
     mbar_init(&bar_s, 1);
-    mbar_init(&bar_p, 2 * kTile);
+    mbar_init(&bar_p, kTile);
     mbar_init(&bar_o, 1);
-    mbar_init(&bar_epi, 2 * kTile);
-    for (int i = 0; i < 4; ++i) mbar_init(&bar_mx[i], 64);  // one per pair of warps that share 32 query rows
-    mbar_init(&bar_l, 2 * kTile);
+    mbar_init(&bar_epi, kTile);
     fence_mbar_init();
   }
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kFwdMmaWarp) {
     tmem_alloc(&tmem_slot, 256);
     tmem_relinquish();
   }
@@ -153,10 +153,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  const uint32_t tS = tmem;         // S fp32 [128 lanes x 128 cols]; P bf16 overlays cols [0,32) and [64,96)
+  const uint32_t tS = tmem;         // S fp32 [128 lanes x 128 cols]; P bf16 overlays cols [0,64)
   const uint32_t tO = tmem + 128;   // O fp32 [128 lanes x D cols]
 
-  if (warp == 8) {
+  if (warp >= 4) {
+    fwd_reg_dec<40>();
+  }
+  if (warp == kFwdProducerWarp) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&mapQ); tma_prefetch_desc(&mapK); tma_prefetch_desc(&mapV);
@@ -172,7 +175,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         for (int s = 0; s < Cfg::kSub; ++s) tma_load_4d(sV + s * 16384, &mapV, &bar_v, s * 64, kb * kTile, h, b);
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kFwdMmaWarp) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
@@ -181,9 +184,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       // 64-column halves; the MN-major operand (V) steps 16 key rows = 2048 B
       constexpr uint32_t hi_k = desc_hi(1024);
       const uint32_t q_lo = desc_lo(smem_u32(sQ), 16), k_lo = desc_lo(smem_u32(sK), 16), v_lo = desc_lo(smem_u32(sV), 16384);
-      bool ok = mbar_wait(&bar_q, 0, &abort_word, 21);
+      // Shared-memory accesses of this thread (barrier waits included) queue behind the MMAs it has issued and only
+      // proceed once the tensor pipe has accepted those, so the wait for the next K tile (normally long complete)
+      // sits two MMAs before the end of the PV group: the pipe stays fed while the wait runs.
+      bool ok = mbar_wait(&bar_q, 0, &abort_word, 21) && mbar_wait(&bar_k, 0, &abort_word, 22);
       for (int j = 0; j < n && ok; ++j) {
-        if (!mbar_wait(&bar_k, j & 1, &abort_word, 22)) break;
 #ifdef TS2TS_STRICT_ORDER
         if (j > 0 && !mbar_wait(&bar_o, (j - 1) & 1, &abort_word, 23)) break;  // P(j-1) consumed before S is overwritten
 #endif
@@ -202,23 +207,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         if (!mbar_wait(&bar_p, j & 1, &abort_word, 25)) break;
         tc_fence_after();
         FTRACE(0, j, 2);
+        constexpr int kSplit = kTile / 16 - 2;
 #pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          mma_ts2(tO, tS + (kk >> 2) * 64 + (kk & 3) * 8, v_lo + kk * (2048 >> 4), hi_k, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < kSplit; ++kk)
+          mma_ts2(tO, tS + kk * 8, v_lo + kk * (2048 >> 4), hi_k, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        if (j + 1 < n && !mbar_wait(&bar_k, (j + 1) & 1, &abort_word, 22)) break;
+#pragma unroll
+        for (int kk = kSplit; kk < kTile / 16; ++kk)
+          mma_ts2(tO, tS + kk * 8, v_lo + kk * (2048 >> 4), hi_k, idesc_pv, 1u);
         mma_commit(&bar_o);
         FTRACE(0, j, 3);
       }
     }
-  } else {
-    // ------------------------------------------------------------------ softmax + epilogue: thread = (query row, half of the key columns)
-    const int row = tid & (kTile - 1), half = tid >> 7;
+  } else if (warp < 4) {
+    // ------------------------------------------------------------------ softmax + epilogue: thread = query row
+    // One thread owns a whole score row: the row maximum and sum need no exchange between threads and the 128
+    // scores are read from tensor memory once and stay in registers between the two sweeps.
+    fwd_reg_inc<216>();
+    const int row = tid;
     const int q = qb * kTile + row;
     const bool q_valid = q < P.T;
     const int mydoc = q_valid ? p.mask.doc[(size_t)b * P.T + q] : INT32_MIN;
     const int myrow = q_valid ? p.mask.row[(size_t)b * P.T + q] : -1;
-    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tSh = tS + lane_base + 64 * half;            // this thread's 64 score columns (later its 32 P columns)
-    const uint32_t tOh = tO + lane_base + (D / 2) * half;       // this thread's half of the accumulator columns
+    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t tSr = tS + lane_base;
+    const uint32_t tOr = tO + lane_base;
     float m_used = -CUDART_INF_F, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n; ++j) {
@@ -236,37 +249,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           }
         }
       }
-      const uint32_t bw0 = half == 0 ? bits[0] : bits[2], bw1 = half == 0 ? bits[1] : bits[3];
       if (tid == 0) FTRACE(1, j, 0);
       if (!(ok = mbar_wait(&bar_s, j & 1, &abort_word, 31))) break;
       tc_fence_after();
       if (tid == 0) FTRACE(1, j, 1);
-      // pass 1: maximum of this thread's 64 masked scores (eight independent running maxima keep the chain short),
-      // then the two halves of a row meet through shared memory
+      uint32_t sv[4][32];
+      tmem_ld32(tSr, sv[0]);
+      tmem_ld32(tSr + 32, sv[1]);
+      tmem_ld32(tSr + 64, sv[2]);
+      tmem_ld32(tSr + 96, sv[3]);
+      tmem_ld_wait();
+      // sweep 1: row maximum (eight independent running maxima keep the dependency chain short)
       float mx8[8];
 #pragma unroll
       for (int i = 0; i < 8; ++i) mx8[i] = -CUDART_INF_F;
+      if (is_full) {
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tSh + c * 32, r);
-        tmem_ld_wait();
-        if (is_full) {
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
-          for (int i = 0; i < 16; ++i) mx8[i & 7] = fmax3(mx8[i & 7], __uint_as_float(r[i]), __uint_as_float(r[i + 16]));
-        } else {
-          const uint32_t bw = c == 0 ? bw0 : bw1;
+          for (int i = 0; i < 16; ++i) mx8[i & 7] = fmax3(mx8[i & 7], __uint_as_float(sv[c][i]), __uint_as_float(sv[c][i + 16]));
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
 #pragma unroll
           for (int i = 0; i < 16; ++i)
-            mx8[i & 7] = fmax3(mx8[i & 7], ((bw >> i) & 1u) ? __uint_as_float(r[i]) : -CUDART_INF_F,
-                               ((bw >> (i + 16)) & 1u) ? __uint_as_float(r[i + 16]) : -CUDART_INF_F);
-        }
+            mx8[i & 7] = fmax3(mx8[i & 7], ((bits[c] >> i) & 1u) ? __uint_as_float(sv[c][i]) : -CUDART_INF_F,
+                               ((bits[c] >> (i + 16)) & 1u) ? __uint_as_float(sv[c][i + 16]) : -CUDART_INF_F);
       }
       float mx = fmax3(fmax3(mx8[0], mx8[1], mx8[2]), fmax3(mx8[3], mx8[4], mx8[5]), fmaxf(mx8[6], mx8[7]));
-      s_mx[j & 1][half][row] = mx;
-      mbar_arrive(&bar_mx[warp & 3]);
-      if (!(ok = mbar_wait(&bar_mx[warp & 3], j & 1, &abort_word, 34))) break;
-      mx = fmaxf(mx, s_mx[j & 1][half ^ 1][row]);
       if (tid == 0) FTRACE(1, j, 2);
       mx *= p.scale_log2;  // scale > 0, so max commutes with the scaling
       const float m_new = fmaxf(m_used, mx);
@@ -275,13 +285,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         const float factor = need ? fast_exp2(m_used - m_new) : 1.f;  // exp2(-inf) = 0 on the first real tile
         if (j > 0) {
 #pragma unroll
-          for (int c = 0; c < D / 64; ++c) {
+          for (int c = 0; c < D / 32; ++c) {
             uint32_t r[32];
-            tmem_ld32(tOh + c * 32, r);
+            tmem_ld32(tOr + c * 32, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * factor);
-            tmem_st32(tOh + c * 32, r);
+            tmem_st32(tOr + c * 32, r);
           }
         }
         l *= factor;
@@ -289,27 +299,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       }
       if (tid == 0) FTRACE(1, j, 3);
       const float m_safe = m_used == -CUDART_INF_F ? 0.f : m_used;
-      // pass 2: P = exp2(s - m), partial row sum (four independent sums), bf16 pack over the columns just read
+      // sweep 2: P = exp2(s - m), row sum (four independent sums), bf16 pack over the first 64 score columns
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t r[32];
-        tmem_ld32(tSh + c * 32, r);
-        tmem_ld_wait();
-        const uint32_t bw = c == 0 ? bw0 : bw1;
+      for (int c = 0; c < 4; ++c) {
         uint32_t pk[16];
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(r[i]), p.scale_log2, -m_safe));
-          float p1 = fast_exp2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, -m_safe));
+          float p0 = fast_exp2(fmaf(__uint_as_float(sv[c][i]), p.scale_log2, -m_safe));
+          float p1 = fast_exp2(fmaf(__uint_as_float(sv[c][i + 1]), p.scale_log2, -m_safe));
           if (!is_full) {
-            p0 = ((bw >> i) & 1u) ? p0 : 0.f;
-            p1 = ((bw >> (i + 1)) & 1u) ? p1 : 0.f;
+            p0 = ((bits[c] >> i) & 1u) ? p0 : 0.f;
+            p1 = ((bits[c] >> (i + 1)) & 1u) ? p1 : 0.f;
           }
           sum4[(i >> 1) & 3] += p0 + p1;
           pk[i >> 1] = pack_bf16(p0, p1);
         }
-        tmem_st16(tSh + c * 16, pk);
+        tmem_st16(tSr + c * 16, pk);
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
       if (tid == 0) FTRACE(1, j, 4);
@@ -318,20 +324,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       mbar_arrive(&bar_p);
       if (tid == 0) FTRACE(1, j, 5);
     }
-    // ---- epilogue: the two half-row sums meet, then O / l -> bf16 -> swizzled smem (Q buffer, free after the last S)
-    //      -> TMA store; each thread converts its half of the accumulator columns
-    s_l[half][row] = l;
-    mbar_arrive(&bar_l);
-    if (ok) ok = mbar_wait(&bar_l, 0, &abort_word, 35);
-    l = s_l[0][row] + s_l[1][row];
+    // ---- epilogue: O / l -> bf16 -> swizzled smem (Q buffer, free after the last S) -> TMA store
     if (ok) ok = mbar_wait(&bar_o, (n - 1) & 1, &abort_word, 32);
     tc_fence_after();
     if (ok) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
+      for (int c = 0; c < D / 32; ++c) {
         uint32_t r[32];
-        tmem_ld32(tOh + c * 32, r);
+        tmem_ld32(tOr + c * 32, r);
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
@@ -340,12 +341,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           v.y = pack_bf16(__uint_as_float(r[g * 8 + 2]) * inv, __uint_as_float(r[g * 8 + 3]) * inv);
           v.z = pack_bf16(__uint_as_float(r[g * 8 + 4]) * inv, __uint_as_float(r[g * 8 + 5]) * inv);
           v.w = pack_bf16(__uint_as_float(r[g * 8 + 6]) * inv, __uint_as_float(r[g * 8 + 7]) * inv);
-          const int chunk = half * (D / 16) + c * 4 + g;  // 16-byte chunk index inside the output row
+          const int chunk = c * 4 + g;  // 16-byte chunk index inside the output row
           *reinterpret_cast<uint4*>(sQ + (chunk >> 3) * 16384 + sw128_offset(row, chunk & 7)) = v;
         }
       }
-      if (q_valid && half == 0)
-        p.lse[((size_t)b * p.H + h) * P.T + q] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
+      if (q_valid) p.lse[((size_t)b * p.H + h) * P.T + q] = l > 0.f ? (m_used + log2f(l)) * 0.6931471805599453f : -CUDART_INF_F;
       fence_async_smem();
       mbar_arrive(&bar_epi);
     }
@@ -363,7 +363,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     if (tid == 0) atomicCAS(P.status, 0, 1000 + abort_word);
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
   }
-  if (warp == 9) tmem_dealloc(tmem, 256);
+  if (warp == kFwdMmaWarp) tmem_dealloc(tmem, 256);
 }
 
 // Host launcher.  Tensor strides are in elements; the last dimension is contiguous.
