@@ -50,16 +50,18 @@ def config5() -> LMConfig:
 
 
 def rope_tables(T: int, head_dim: int, base: float, device, dtype=torch.float32):
+    """cos and sin of the rotation angles, both halves filled: [T, head_dim] each, computed in fp32."""
     inv = 1.0 / (base ** (torch.arange(0, head_dim, 2, device=device, dtype=torch.float32) / head_dim))
     ang = torch.arange(T, device=device, dtype=torch.float32)[:, None] * inv[None, :]
-    return ang.cos().to(dtype), ang.sin().to(dtype)
+    return torch.cat([ang.cos(), ang.cos()], dim=-1).to(dtype), torch.cat([ang.sin(), ang.sin()], dim=-1).to(dtype)
 
 
 def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
-    """x [B,H,T,D]; rotate pairs (first half, second half)."""
+    """x [..., T, *, *, D] with cos / sin broadcastable to it; rotates pairs (first half, second half) in x's dtype:
+    x * cos + rotate_half(x) * sin with rotate_half(x) = (-x2, x1)."""
     h = x.shape[-1] // 2
-    x1, x2 = x[..., :h], x[..., h:]
-    return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
+    rot = torch.cat([-x[..., h:], x[..., :h]], dim=-1)
+    return x * cos + rot * sin
 
 
 class Block(nn.Module):
@@ -78,8 +80,8 @@ class Block(nn.Module):
         B, T, _ = x.shape
         c = self.cfg
         qkv = self.qkv(self.ln1(x)).view(B, T, 3, c.n_heads, c.head_dim)
-        q, k, v = (qkv[:, :, i].permute(0, 2, 1, 3) for i in range(3))          # [B,H,T,D] strided views
-        q, k = apply_rope(q, cos, sin).to(v.dtype), apply_rope(k, cos, sin).to(v.dtype)
+        qk = apply_rope(qkv[:, :, :2], cos, sin)                                # q and k rotated together, [B,T,2,H,D]
+        q, k, v = qk[:, :, 0].permute(0, 2, 1, 3), qk[:, :, 1].permute(0, 2, 1, 3), qkv[:, :, 2].permute(0, 2, 1, 3)  # [B,H,T,D] strided views
         out, _ = masked_attn(q, k, v, mask.doc_ids, mask.link_bits, q_row_ids=mask.q_row_ids, kv_col_ids=mask.kv_col_ids,
                              plan=mask.plan)                                      # x + attn(ln(x)), layer.py:32-35
         x = x + self.proj(out.transpose(1, 2).reshape(B, T, c.n_heads * c.head_dim))
@@ -103,8 +105,9 @@ class DecoderLM(nn.Module):
         """tokens int64 [B, T+1]; returns the mean next-token cross-entropy (training_module.py:195-211)."""
         inp, tgt = tokens[:, :-1], tokens[:, 1:]
         T = inp.shape[1]
-        cos, sin = rope_tables(T, self.cfg.head_dim, self.cfg.rope_base, inp.device)
         x = self.embed(inp)
+        cos, sin = (t.to(x.dtype if not torch.is_autocast_enabled() else torch.get_autocast_dtype("cuda"))[None, :, None, None, :]
+                    for t in rope_tables(T, self.cfg.head_dim, self.cfg.rope_base, inp.device))
         for blk in self.blocks:
             x = blk(x, mask, cos, sin)
         logits = self.head(self.norm(x))
