@@ -505,11 +505,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       if (!(ok = mbar_wait(&bar_g, i & 1, abort_w, 41))) break;
       tc_fence_after();
       if (tid == 2 * kTile) TRACE(2, i, 0);
-      uint32_t r[4][32];
-      tmem_ld32(tDPT + lane_base, r[0]);
-      tmem_ld32(tDPT + lane_base + 32, r[1]);
-      tmem_ld32(tDPT + lane_base + 64, r[2]);
-      tmem_ld32(tDPT + lane_base + 96, r[3]);
+      uint32_t r[2][64];
+      tmem_ld64(tDPT + lane_base, r[0]);
+      tmem_ld64(tDPT + lane_base + 64, r[1]);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&bar_dqr);  // the dP^T / dQ^T columns may be overwritten once all four warps have arrived
@@ -526,7 +524,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         uint8_t* base = buf + word * 4;
 #pragma unroll
         for (int c = 0; c < 32; ++c)
-          *reinterpret_cast<float*>(base + c * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r[k][c]) * p.scale;
+          *reinterpret_cast<float*>(base + c * 128 + ((chunk ^ (c & 7)) << 4)) = __uint_as_float(r[k >> 1][32 * (k & 1) + c]) * p.scale;
         fence_async_smem();
         __syncwarp();
         if (lane == 0) {
