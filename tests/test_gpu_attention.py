@@ -66,6 +66,17 @@ def test_small_cases(t, h, d, p):
     _run_case(t, h, d, p, seed=t + d)
 
 
+def test_random_shapes_and_document_statistics():
+    """Seeded sweep over ragged lengths around the tile edges, both head sizes, batches, link densities and document
+    lengths from a few tokens to longer than a tile."""
+    import random
+    rng = random.Random(2024)
+    for it in range(16):
+        t = rng.choice([5, 64, 127, 129, 255, 257, 383, 511, 640, 777, 1024, 1500])
+        _run_case(t, rng.choice([1, 2, 3]), rng.choice([64, 128]), rng.choice([0.0, 0.1, 0.5]), seed=7000 + 10 * it,
+                  median=rng.choice([3, 20, 100, 400]), lo=1, hi=max(2, t), batch=rng.choice([1, 2]))
+
+
 def test_config1_shape_doc_causal():
     """The CPU-runnable configuration: B=1, T=2048, H=8, D=64, doc_causal, median 128 in [16,512]."""
     _run_case(2048, 8, 64, 0.0, seed=1001, median=128, lo=16, hi=512)
