@@ -285,8 +285,8 @@ def run_ours(args, rank, world, device):
         "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel<128>", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": achieved / peak_tf, "peak_kind": peak_kind + " (burst)", "avg_launch_ms": bwd_ms,
                      "algorithmic_flops_per_launch": bwd_flops,
-                     # dram read+write bytes per launch: ncu capture of the 16k case (641.3 MB, profiles/), scaled by B*H*T
-                     "traffic": 641.3e6 * (B * H * T) / (1 * 16 * 16384) if D == 128 else None,
+                     # dram read+write bytes per launch: ncu capture of the 16k case (633.6 MB, profiles/), scaled by B*H*T
+                     "traffic": 633.6e6 * (B * H * T) / (1 * 16 * 16384) if D == 128 else None,
                      "fwd": {"achieved": sum(4.0 * D * H * m["pairs"] for m in masks) / sum(p["fwd_ms"] for p in per_mask) / 1e9,
                              "avg_launch_ms": statistics.mean(p["fwd_ms"] for p in per_mask)}},
     }
