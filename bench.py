@@ -294,7 +294,73 @@ def run_ours(args, rank, world, device):
         line["cpu_baseline"] = cpu_baseline(steps=1)
     if train is not None:
         line["train_step"] = train
+    if world == 1:
+        line["link_scan"] = link_scan_bench(device)
     emit(line)
+
+
+def link_scan_bench(device, _unused=None):
+    """Device-side markdown link scan (ts2ts_detect_links) on synthetic GPT-2-sized token streams: uniform random ids
+    with a '](' planted every ~200 tokens behind a '[' and in front of a closing token.  The real GPT-2 table of
+    tokens that contain ')' needs the BPE files, so a synthetic table stands in for it (every 97th id closes a link).
+    Reports the scan at the 32k sequence length of the workload (latency-bound) and on a 1 Mi-token stream against the
+    measured HBM copy bandwidth, with the oracle's pure-Python scan of the 32k stream timed beside it."""
+    from tagseq2tagseq_b200 import _lib
+    from oracle import link_detect as old
+    L = _lib.lib()
+    _, hbm_gbs, peak_kind = measured_peaks()
+    vocab, mid, starts = 50257, 16151, [58, 685]
+    rng = np.random.default_rng(77)
+    flags_np = (np.arange(vocab) % 97 == 0).astype(np.uint8)
+    closers = np.nonzero(flags_np)[0]
+    out = {"vocab": vocab, "note": "synthetic close-token table (every 97th id)"}
+    for name, n_tok in (("32k", 32768), ("1Mi", 1 << 20)):
+        toks = rng.integers(1000, vocab, size=n_tok, dtype=np.int64)
+        toks[np.isin(toks, [mid] + starts)] = 1000
+        for pos in range(50, n_tok - 60, 200):
+            toks[pos] = starts[pos // 200 % 2]
+            toks[pos + 5] = mid
+            toks[pos + 5 + 1 + (pos // 200) % 9] = closers[(pos // 200) % len(closers)]
+        tok_d = torch.from_numpy(toks).to(device)
+        flags_d = torch.from_numpy(flags_np).to(device)
+        scratch = torch.empty(L.ts2ts_detect_links_scratch_bytes(n_tok), dtype=torch.uint8, device=device)
+        max_links = n_tok // 64
+        links = torch.empty((max_links, 3), dtype=torch.int32, device=device)
+        count = torch.zeros(1, dtype=torch.int32, device=device)
+        start_arr = (ctypes.c_int64 * 2)(*starts)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+        def call():
+            rc = L.ts2ts_detect_links(tok_d.data_ptr(), 8, n_tok, mid, start_arr, 2, flags_d.data_ptr(), vocab, 100, 50,
+                                      scratch.data_ptr(), scratch.numel(), links.data_ptr(), max_links, count.data_ptr(), stream)
+            if rc != 0:
+                raise RuntimeError(L.ts2ts_last_error_string().decode())
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        reps = 50
+        e0.record()
+        for _ in range(reps):
+            call()
+        e1.record()
+        torch.cuda.synchronize(device)
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        res = {"tokens": n_tok, "links": int(count.item()), "us_per_call": us, "gpu_launches_per_call": 3,
+               "token_gbs": n_tok * 8 / us / 1e3}
+        if name == "1Mi":
+            # algorithmic bytes: tokens read once (8 B) + dense marks written and read once (2 x 8 B)
+            res["roofline"] = {"bound": "hbm", "achieved": n_tok * 24 / us / 1e3, "peak": hbm_gbs, "unit": "GB/s",
+                               "frac": n_tok * 24 / us / 1e3 / hbm_gbs, "peak_kind": peak_kind}
+        else:
+            decode = lambda ids: "".join(")" if flags_np[i] else "a" for i in ids)
+            t0 = time.perf_counter()
+            want = old.candidates(toks.tolist(), decode, mid_id=mid, start_ids=starts, window=50)
+            res["cpu_port_us"] = (time.perf_counter() - t0) * 1e6
+            got = links[:int(count.item())].cpu().tolist()
+            res["matches_oracle"] = [tuple(g) for g in got] == want
+        out[name] = res
+    return out
 
 
 def run_train(args, rank, world, device, which: str, steps: int, warmup: int):

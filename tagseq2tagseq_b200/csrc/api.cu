@@ -202,7 +202,7 @@ int ts2ts_attn_bwd_noalloc(const void* q, const void* k, const void* v, const vo
 
 size_t ts2ts_detect_links_scratch_bytes(int T) {
   if (T <= 0 || T > kMaxT) return 0;
-  return (static_cast<size_t>(T) * 2 * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
+  return (link_scan_scratch_ints(T) * sizeof(int32_t) + 255) & ~static_cast<size_t>(255);
 }
 
 int ts2ts_detect_links(const void* tokens, int token_bytes, int T, int64_t mid_id, const int64_t* start_ids, int n_start,

@@ -20,7 +20,8 @@ struct LinkScanArgs {
   int window;
 };
 
-// `scratch` holds 2*T int32.  Launches on `stream`; returns the launch status.
+// `scratch` holds link_scan_scratch_ints(T) int32.  Launches on `stream`; returns the launch status.
+size_t link_scan_scratch_ints(int T);
 cudaError_t launch_link_scan(const LinkScanArgs& a, int32_t* scratch, int32_t* out, int max_links, int32_t* count,
                              cudaStream_t stream);
 
