@@ -177,7 +177,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint64_t& bar_dqr = bars[9];         // dQ^T read out of tensor memory
   uint64_t& bar_epi = bars[10];
   uint64_t& bar_s = bars[12];          // S^T of the tile is in tensor memory (dP^T may still be running)
-  uint64_t& bar_issued = bars[11];     // S^T and dP^T MMAs of the tile handed to the tensor pipe
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_ptr = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars + 16) + 4);
   int* abort_w = const_cast<int*>(abort_ptr);
@@ -224,7 +223,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     mbar_init(&bar_g, 1);
     mbar_init(&bar_dqr, kTile);
     mbar_init(&bar_epi, 2 * kTile);
-    mbar_init(&bar_issued, 1);
     mbar_init(&bar_s, 1);
     fence_mbar_init();
   }
@@ -304,7 +302,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           mma_ss2(tDPT, v_kmaj + off, hi, do_kmaj + off, hi, idesc_st, kk > 0);
         }
         mma_commit(&bar_st);
-        mbar_arrive(&bar_issued);
       };
       auto issue_dqt = [&]() {  // dQ^T = K^T dS^T   (K = 128 keys; M = D, padded to 128 lanes when D = 64)
 #pragma unroll
@@ -495,10 +492,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const int box = dlane >> 5, chunk = (dlane & 31) >> 2, word = dlane & 3;
     const bool has_box = box * 32 < D;
     uint8_t* my_stage = sStage + (warp & 3) * 8192;
-    // The warp on the MMA issuer's scheduler partition shares that partition's memory-instruction queue with it:
-    // its stores would be interleaved with the S^T / dP^T MMAs of the next tile and slow their issue.  It holds its
-    // values in registers until dP^T of the next tile has been handed over.
-    const bool behind_issuer = (warp & 3) == (13 & 3);
     bool ok = true;
     for (int i = 0; i < n; ++i) {
       const int qb = list[i] & ~kFullBit;
@@ -513,7 +506,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       mbar_arrive(&bar_dqr);  // the dP^T / dQ^T columns may be overwritten once all four warps have arrived
       if (tid == 2 * kTile) TRACE(2, i, 1);
       if (!has_box) continue;
-      if (behind_issuer && i + 1 < n && !(ok = mbar_wait(&bar_issued, (i + 1) & 1, abort_w, 43))) break;
       if (tid == 2 * kTile) TRACE(2, i, 3);
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
