@@ -299,7 +299,7 @@ def run_ours(args, rank, world, device):
     emit(line)
 
 
-def link_scan_bench(device, _unused=None):
+def link_scan_bench(device):
     """Device-side markdown link scan (ts2ts_detect_links) on synthetic GPT-2-sized token streams: uniform random ids
     with a '](' planted every ~200 tokens behind a '[' and in front of a closing token.  The real GPT-2 table of
     tokens that contain ')' needs the BPE files, so a synthetic table stands in for it (every 97th id closes a link).
