@@ -232,7 +232,9 @@ int ts2ts_read_status(const void* plan, void* stream, int32_t* status_out) {
   cudaError_t e = cudaMemcpyAsync(status_out, plan, sizeof(int32_t), cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream));
   if (e == cudaSuccess) e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(-60, "status read failed: %s", cudaGetErrorString(e));
-  if (*status_out != 0) fail(*status_out, "a kernel gave up a bounded wait (code %d)", *status_out);
+  if (*status_out != 0)
+    return fail(*status_out > 0 ? *status_out : -61, "a kernel recorded status %d (19xx / 29xx: the plan was not built for this call; "
+                "otherwise 1000 / 2000 + the wait that ran out in the forward / backward kernel)", *status_out);
   return 0;
 }
 

@@ -180,9 +180,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_ptr = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars + 16) + 4);
   int* abort_w = const_cast<int*>(abort_ptr);
-  if (smem + Cfg::kTiles + Cfg::kSmall > smem_raw + Cfg::kBytes) {  // uniform across the CTA
-    if (threadIdx.x == 0) atomicCAS(p.plan.status, 0, 2900);
-    return;
+  {  // uniform across the grid: refuse a plan that was not built for this (B, T), or a misplaced shared-memory window
+    int bad = 0;
+    const int32_t* stw = p.plan.status;
+    if (stw[kStampMagic] != kPlanMagic || stw[kStampB] != p.plan.B || stw[kStampT] != p.plan.T) bad = 2901;
+    else if (smem + Cfg::kTiles + Cfg::kSmall > smem_raw + Cfg::kBytes) bad = 2900;
+    if (bad) {
+      if (threadIdx.x == 0) atomicCAS(p.plan.status, 0, bad);
+      return;
+    }
   }
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -191,8 +197,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   const int rank = blockIdx.x % NB;
   const int bh = blockIdx.x / NB;
   const int h = bh % p.H, b = bh / p.H;
-  const int kb = P.bwd_order[(size_t)b * NB + rank];
-  const int n = P.bwd_cnt[(size_t)b * NB + kb];
+  const int kb = min(max(P.bwd_order[(size_t)b * NB + rank], 0), NB - 1);
+  const int n = min(max(P.bwd_cnt[(size_t)b * NB + kb], 0), NB);
   const int32_t* list = P.bwd_idx + ((size_t)b * NB + kb) * NB;
 
   if (n == 0) {

@@ -115,20 +115,41 @@ __global__ void __launch_bounds__(128) lists_kernel(PlanView P, int transposed, 
   }
 }
 
+// Forward work items are pairs of adjacent q tiles (2p, 2p+1) that share one stream of K/V tiles: count the kv
+// tiles at least one of the two reads.  One thread per (pair, b).
+__global__ void __launch_bounds__(128) pair_count_kernel(PlanView P) {
+  const int pr = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  const int NP = (P.NB + 1) / 2;
+  if (pr >= NP) return;
+  const uint8_t* s0 = P.state + ((size_t)b * P.NB + 2 * pr) * P.NB;
+  const uint8_t* s1 = (2 * pr + 1 < P.NB) ? s0 + P.NB : s0;
+  int n = 0;
+  for (int kb = 0; kb <= min(2 * pr + 1, P.NB - 1); ++kb) n += (s0[kb] | s1[kb]) != kSkip;
+  P.pair_cnt[(size_t)b * NP + pr] = n;
+}
+
 // Heaviest-first order inside each batch element: rank by descending count, ties by index.
+// which = 0: q tiles by fwd_cnt, 1: kv tiles by bwd_cnt, 2: q-tile pairs by pair_cnt.
 __global__ void __launch_bounds__(256) order_kernel(PlanView P) {
   const int b = blockIdx.y, which = blockIdx.z;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= P.NB) return;
-  const int32_t* cnt = (which ? P.bwd_cnt : P.fwd_cnt) + (size_t)b * P.NB;
-  int32_t* order = (which ? P.bwd_order : P.fwd_order) + (size_t)b * P.NB;
+  const int n = which == 2 ? (P.NB + 1) / 2 : P.NB;
+  if (i >= n) return;
+  const int32_t* cnt = (which == 2 ? P.pair_cnt : which == 1 ? P.bwd_cnt : P.fwd_cnt) + (size_t)b * n;
+  int32_t* order = (which == 2 ? P.pair_order : which == 1 ? P.bwd_order : P.fwd_order) + (size_t)b * n;
   const int ci = cnt[i];
   int rank = 0;
-  for (int j = 0; j < P.NB; ++j) {
+  for (int j = 0; j < n; ++j) {
     const int cj = cnt[j];
     rank += (cj > ci) || (cj == ci && j < i);
   }
   order[rank] = i;
+}
+
+__global__ void stamp_kernel(PlanView P) {
+  P.status[kStampMagic] = kPlanMagic;
+  P.status[kStampB] = P.B;
+  P.status[kStampT] = P.T;
 }
 
 // Host entry: fills the plan; optional BlockMask-shaped outputs may be null.
@@ -141,7 +162,9 @@ cudaError_t launch_block_map(PlanView P, MaskArgs M, uint8_t* state_out, int32_t
   state_kernel<<<dim3((P.NB + 127) / 128, P.NB, P.B), 128, 0, stream>>>(P, M);
   lists_kernel<<<dim3((P.NB + 3) / 4, P.B), 128, 0, stream>>>(P, 0, kv_cnt, kv_idx, full_cnt, full_idx);
   lists_kernel<<<dim3((P.NB + 3) / 4, P.B), 128, 0, stream>>>(P, 1, q_cnt, q_idx, full_q_cnt, full_q_idx);
-  order_kernel<<<dim3((P.NB + 255) / 256, P.B, 2), 256, 0, stream>>>(P);
+  pair_count_kernel<<<dim3(((P.NB + 1) / 2 + 127) / 128, P.B), 128, 0, stream>>>(P);
+  order_kernel<<<dim3((P.NB + 255) / 256, P.B, 3), 256, 0, stream>>>(P);
+  stamp_kernel<<<1, 1, 0, stream>>>(P);
   if (state_out)
     cudaMemcpyAsync(state_out, P.state, (size_t)P.B * P.NB * P.NB, cudaMemcpyDeviceToDevice, stream);
   return cudaGetLastError();

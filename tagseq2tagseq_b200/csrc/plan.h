@@ -22,9 +22,19 @@ struct alignas(16) Run {
 
 constexpr uint32_t kFullBit = 1u << 30;  // set in merged list entries for full tiles
 
+// Words of the status block.  Word 0 holds the first device error code.  The stamp is written by the pre-pass and
+// compared by every attention kernel with its own B and T before it touches a list.  The ticket / done words are
+// the work counters of the persistent attention kernels: a CTA draws work items from `ticket`; the last CTA to
+// leave (counted in `done`) puts both back to zero, so launches that share a plan must be ordered on one stream.
+enum : int {
+  kStatusCode = 0, kStampMagic = 1, kStampB = 2, kStampT = 3,
+  kFwdTicket = 8, kFwdDone = 9, kBwdTicket = 10, kBwdDone = 11,
+};
+constexpr int32_t kPlanMagic = 0x54533254;  // "TS2T"
+
 struct PlanLayout {
   int B, T, NB;
-  size_t status;      // int32[64]   word 0: first device error code, word 1.. totals
+  size_t status;      // int32[64]   see the kStatus* / kStamp* / k*Ticket words above
   size_t run_cnt;     // int32[B,NB]
   size_t runs;        // Run[B,NB,128]
   size_t state;       // uint8[B,NB,NB]   state[b,qb,kb]
@@ -34,6 +44,8 @@ struct PlanLayout {
   size_t bwd_idx;     // int32[B,NB,NB]   ascending qb, kFullBit set when full
   size_t fwd_order;   // int32[B,NB]      q tiles of batch b by descending fwd_cnt
   size_t bwd_order;   // int32[B,NB]      kv tiles of batch b by descending bwd_cnt
+  size_t pair_cnt;    // int32[B,NP]      NP = ceil(NB/2): kv tiles that q tile 2p or 2p+1 reads (forward work items)
+  size_t pair_order;  // int32[B,NP]      pairs of batch b by descending pair_cnt
   size_t bytes;
 };
 
@@ -56,6 +68,9 @@ inline PlanLayout plan_layout(int B, int T) {
   L.bwd_idx = off;   off = plan_align(off + b * nb * nb * sizeof(int32_t));
   L.fwd_order = off; off = plan_align(off + b * nb * sizeof(int32_t));
   L.bwd_order = off; off = plan_align(off + b * nb * sizeof(int32_t));
+  const size_t np = (nb + 1) / 2;
+  L.pair_cnt = off;   off = plan_align(off + b * np * sizeof(int32_t));
+  L.pair_order = off; off = plan_align(off + b * np * sizeof(int32_t));
   L.bytes = off;
   return L;
 }
@@ -73,6 +88,8 @@ struct PlanView {
   int32_t* bwd_idx;
   int32_t* fwd_order;
   int32_t* bwd_order;
+  int32_t* pair_cnt;
+  int32_t* pair_order;
 };
 
 inline PlanView plan_view(void* base, int B, int T) {
@@ -90,6 +107,8 @@ inline PlanView plan_view(void* base, int B, int T) {
   v.bwd_idx = reinterpret_cast<int32_t*>(p + L.bwd_idx);
   v.fwd_order = reinterpret_cast<int32_t*>(p + L.fwd_order);
   v.bwd_order = reinterpret_cast<int32_t*>(p + L.bwd_order);
+  v.pair_cnt = reinterpret_cast<int32_t*>(p + L.pair_cnt);
+  v.pair_order = reinterpret_cast<int32_t*>(p + L.pair_order);
   return v;
 }
 

@@ -45,8 +45,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait.  `abort_word` lives in shared memory; once it is non-zero every
-// later wait returns false immediately so the CTA can drain and leave.
+// later wait on a phase that is not complete yet returns false immediately so the CTA can drain and leave.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_word, int code) {
+  if (mbar_try_wait(bar, parity)) return true;  // the common case costs one shared-memory round trip
   if (*abort_word) return false;
   for (uint32_t i = 0; i < TS2TS_SPIN_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -94,6 +95,8 @@ __device__ __forceinline__ void tma_reduce_add_4d(const void* tmap, const void* 
 }
 __device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// None of this thread's bulk groups is still reading its shared-memory source afterwards.
+__device__ __forceinline__ void tma_store_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // At most one of this thread's bulk groups may still be reading its shared-memory source afterwards.
 __device__ __forceinline__ void tma_store_wait_read1() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 
@@ -234,6 +237,46 @@ __device__ __forceinline__ void tmem_ld64(uint32_t taddr, uint32_t (&r)[64]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ----------------------------------------------------------------------------- packed fp32 arithmetic (two lanes per instruction)
+__device__ __forceinline__ unsigned long long pack_f32x2(float lo, float hi) {
+  unsigned long long r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack_f32x2(unsigned long long v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ unsigned long long fma_f32x2(unsigned long long a, unsigned long long b, unsigned long long c) {
+  unsigned long long d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+__device__ __forceinline__ unsigned long long add_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ unsigned long long mul_f32x2(unsigned long long a, unsigned long long b) {
+  unsigned long long d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+
+// ----------------------------------------------------------------------------- prefetching loads
+// Read-only global loads that stay where they are written.  A plain load whose value is first used an iteration
+// later may be moved down to that use by the compiler (it frees registers), which turns a prefetch into a stall
+// of one L2 round trip; a volatile asm statement is issued in program order.
+__device__ __forceinline__ int ld_nc_i32_here(const int32_t* ptr) {
+  int v;
+  asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(ptr));
+  return v;
+}
+__device__ __forceinline__ int4 ld_nc_v4_here(const void* ptr) {
+  int4 v;
+  asm volatile("ld.global.nc.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
+  return v;
+}
 
 // ----------------------------------------------------------------------------- misc
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {

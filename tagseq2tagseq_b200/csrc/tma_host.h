@@ -6,6 +6,9 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <string.h>
+
+#include <mutex>
 
 namespace ts2ts {
 
@@ -44,6 +47,47 @@ inline int make_tile_map(CUtensorMap* out, const void* base, int elem_bytes, int
   CUresult r = enc(out, dt, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -103;
+}
+
+// The same map through a small per-process cache: a training step calls the attention entry points once per layer
+// with the same few (pointer, shape, strides) combinations, and encoding a map costs a driver call each time.
+// The returned pointer stays valid until kMapCacheSize other maps have been requested; a launch copies the map
+// into its kernel parameters before it returns, so callers use it for one launch only.
+constexpr int kMapCacheSize = 64;
+struct MapKey {
+  const void* base;
+  int64_t v[9];
+  int dev;
+};
+inline int cached_tile_map(const CUtensorMap** out, const void* base, int elem_bytes, int64_t B, int64_t H, int64_t T, int64_t D,
+                           int64_t sb, int64_t sh, int64_t st, int box_rows, int box_cols) {
+  struct Entry { MapKey key; CUtensorMap map; bool used; };
+  static Entry cache[kMapCacheSize];
+  static int next = 0;
+  static std::mutex mu;
+  MapKey key;
+  memset(&key, 0, sizeof(key));
+  key.base = base;
+  const int64_t vals[9] = {elem_bytes, B, H, T, D, sb, sh, st, (int64_t)box_rows * 65536 + box_cols};
+  for (int i = 0; i < 9; ++i) key.v[i] = vals[i];
+  cudaGetDevice(&key.dev);
+  std::lock_guard<std::mutex> lock(mu);
+  for (int i = 0; i < kMapCacheSize; ++i)
+    if (cache[i].used && memcmp(&cache[i].key, &key, sizeof(key)) == 0) {
+      *out = &cache[i].map;
+      return 0;
+    }
+  Entry& e = cache[next];
+  const int r = make_tile_map(&e.map, base, elem_bytes, B, H, T, D, sb, sh, st, box_rows, box_cols);
+  if (r) {
+    e.used = false;
+    return r;
+  }
+  e.key = key;
+  e.used = true;
+  *out = &e.map;
+  next = (next + 1) % kMapCacheSize;
+  return 0;
 }
 
 }  // namespace ts2ts

@@ -113,8 +113,9 @@ def read_status(plan: torch.Tensor) -> int:
     out = ctypes.c_int32(0)
     with torch.cuda.device(plan.device):
         code = _lib.lib().ts2ts_read_status(plan.data_ptr(), torch.cuda.current_stream(plan.device).cuda_stream, ctypes.byref(out))
-    _lib.check(code, "ts2ts_read_status")
-    return int(out.value)
+    if code < 0:
+        _lib.check(code, "ts2ts_read_status")
+    return int(out.value)  # a positive return value is the recorded code itself
 
 
 @dataclass
