@@ -29,9 +29,18 @@
 #include "tma_host.h"
 
 #include <math_constants.h>
-#ifdef TS2TS_TRACE
-#include <stdio.h>
-#include <stdlib.h>
+
+// A debug build may name a private header that defines the hooks below to record clock64() stamps.
+#ifdef TS2TS_BWD_TRACE_HEADER
+#include TS2TS_BWD_TRACE_HEADER
+#else
+#define TS2TS_BWD_TRACE_FIELDS
+#define TRACE(role, step, ev) do { } while (0)
+#define BTRACE_ACC_DECL
+#define BTRACE_ACC(k) do { } while (0)
+#define BTRACE_ACC_DUMP() do { } while (0)
+#define BTRACE_ATTACH(params, stream) do { } while (0)
+#define BTRACE_DUMP(stream) do { } while (0)
 #endif
 
 namespace ts2ts {
@@ -47,22 +56,20 @@ struct BwdParams {
   int64_t dk_s[3], dv_s[3];
   int H, Tp;
   float scale, scale_log2;
-#ifdef TS2TS_TRACE
-  long long* trace;
-  unsigned trace_block;
-#endif
+  TS2TS_BWD_TRACE_FIELDS
 };
-
-#ifdef TS2TS_TRACE
-// Debug build only: per-role clock64() stamps of one CTA, written to a buffer the launcher allocates.
-#define TRACE(role, step, ev) do { if (p.trace && blockIdx.x == p.trace_block) { \
-  long long* t_ = p.trace + ((((role) * 64 + ((step) & 63)) * 8 + (ev))); *t_ = clock64(); } } while (0)
-#else
-#define TRACE(role, step, ev) do { } while (0)
-#endif
 
 constexpr int kBwdThreads = 512;  // warps 0-7 exp/dS, 8-11 dQ reduction, 12 TMA producer, 13 MMA issuer, 14-15 idle
 constexpr int kSubQ = 64;         // query columns per compute half
+#ifndef TS2TS_BWD_X2
+#define TS2TS_BWD_X2 1
+#endif
+#ifndef TS2TS_BWD_LD2
+#define TS2TS_BWD_LD2 0
+#endif
+#ifndef TS2TS_BWD_ELECT
+#define TS2TS_BWD_ELECT 1
+#endif
 
 template <int D>
 struct BwdSmem {
@@ -116,16 +123,34 @@ __device__ __forceinline__ void allowed_rows(const PlanView& P, const MaskArgs& 
 //             registers for the second phase)
 //   ds_chunk  dS^T = P^T (dP^T - delta), from the bf16 P^T, packed to bf16 pairs
 // The row statistics of the 32 queries are read from shared memory; every lane of a warp reads the same addresses.
-__device__ __forceinline__ void p_chunk(const uint32_t (&s)[32], const float* l2, uint32_t bw, bool masked, float scale_log2,
+// `nl2` / `ndl` hold the NEGATED statistics (-lse2, -delta), so that both phases are one packed multiply-add /
+// add per two queries (fp32x2 instructions; a 16-byte shared-memory load yields two ready operand pairs).
+// mode: 0 = every query allowed, 1 = test the bits of `bw`, 2 = no query allowed (nothing is computed).
+__device__ __forceinline__ void p_chunk(const uint32_t (&s)[32], const float* nl2, uint32_t bw, int mode, float scale_log2,
                                         uint32_t (&pk)[16]) {
+  if (mode == 2) {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) pk[e] = 0u;
+    return;
+  }
+  const unsigned long long scale2 = pack_f32x2(scale_log2, scale_log2);
 #pragma unroll
   for (int e = 0; e < 32; e += 4) {
-    const float4 l4 = *reinterpret_cast<const float4*>(l2 + e);
-    float p0 = fast_exp2(fmaf(__uint_as_float(s[e + 0]), scale_log2, -l4.x));
-    float p1 = fast_exp2(fmaf(__uint_as_float(s[e + 1]), scale_log2, -l4.y));
-    float p2 = fast_exp2(fmaf(__uint_as_float(s[e + 2]), scale_log2, -l4.z));
-    float p3 = fast_exp2(fmaf(__uint_as_float(s[e + 3]), scale_log2, -l4.w));
-    if (masked) {
+    const ulonglong2 n4 = *reinterpret_cast<const ulonglong2*>(nl2 + e);
+    float x0, x1, x2, x3;
+#if TS2TS_BWD_X2
+    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[e + 0]), __uint_as_float(s[e + 1])), scale2, n4.x), x0, x1);
+    unpack_f32x2(fma_f32x2(pack_f32x2(__uint_as_float(s[e + 2]), __uint_as_float(s[e + 3])), scale2, n4.y), x2, x3);
+#else
+    {
+      float n0, n1, n2, n3;
+      unpack_f32x2(n4.x, n0, n1); unpack_f32x2(n4.y, n2, n3);
+      x0 = fmaf(__uint_as_float(s[e + 0]), scale_log2, n0); x1 = fmaf(__uint_as_float(s[e + 1]), scale_log2, n1);
+      x2 = fmaf(__uint_as_float(s[e + 2]), scale_log2, n2); x3 = fmaf(__uint_as_float(s[e + 3]), scale_log2, n3);
+    }
+#endif
+    float p0 = fast_exp2(x0), p1 = fast_exp2(x1), p2 = fast_exp2(x2), p3 = fast_exp2(x3);
+    if (mode == 1) {
       p0 = ((bw >> (e + 0)) & 1u) ? p0 : 0.f;
       p1 = ((bw >> (e + 1)) & 1u) ? p1 : 0.f;
       p2 = ((bw >> (e + 2)) & 1u) ? p2 : 0.f;
@@ -135,15 +160,34 @@ __device__ __forceinline__ void p_chunk(const uint32_t (&s)[32], const float* l2
     pk[(e >> 1) + 1] = pack_bf16(p2, p3);
   }
 }
-__device__ __forceinline__ void ds_chunk(const uint32_t (&pk)[16], const uint32_t (&dp)[32], const float* dl, uint32_t (&dsk)[16]) {
+__device__ __forceinline__ void ds_chunk(const uint32_t (&pk)[16], const uint32_t (&dp)[32], const float* ndl, int mode,
+                                         uint32_t (&dsk)[16]) {
+  if (mode == 2) {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) dsk[e] = 0u;
+    return;
+  }
 #pragma unroll
   for (int e = 0; e < 32; e += 4) {
-    const float4 d4 = *reinterpret_cast<const float4*>(dl + e);
+    const ulonglong2 d4 = *reinterpret_cast<const ulonglong2*>(ndl + e);
     const uint32_t a = pk[(e >> 1) + 0], c = pk[(e >> 1) + 1];
-    const float p0 = __uint_as_float(a << 16), p1 = __uint_as_float(a & 0xffff0000u);
-    const float p2 = __uint_as_float(c << 16), p3 = __uint_as_float(c & 0xffff0000u);
-    dsk[(e >> 1) + 0] = pack_bf16(p0 * (__uint_as_float(dp[e + 0]) - d4.x), p1 * (__uint_as_float(dp[e + 1]) - d4.y));
-    dsk[(e >> 1) + 1] = pack_bf16(p2 * (__uint_as_float(dp[e + 2]) - d4.z), p3 * (__uint_as_float(dp[e + 3]) - d4.w));
+    const unsigned long long p01 = pack_f32x2(__uint_as_float(a << 16), __uint_as_float(a & 0xffff0000u));
+    const unsigned long long p23 = pack_f32x2(__uint_as_float(c << 16), __uint_as_float(c & 0xffff0000u));
+    float r0, r1, r2, r3;
+#if TS2TS_BWD_X2
+    unpack_f32x2(mul_f32x2(p01, add_f32x2(pack_f32x2(__uint_as_float(dp[e + 0]), __uint_as_float(dp[e + 1])), d4.x)), r0, r1);
+    unpack_f32x2(mul_f32x2(p23, add_f32x2(pack_f32x2(__uint_as_float(dp[e + 2]), __uint_as_float(dp[e + 3])), d4.y)), r2, r3);
+#else
+    {
+      float n0, n1, n2, n3, q0, q1, q2, q3;
+      unpack_f32x2(d4.x, n0, n1); unpack_f32x2(d4.y, n2, n3);
+      unpack_f32x2(p01, q0, q1); unpack_f32x2(p23, q2, q3);
+      r0 = q0 * (__uint_as_float(dp[e + 0]) + n0); r1 = q1 * (__uint_as_float(dp[e + 1]) + n1);
+      r2 = q2 * (__uint_as_float(dp[e + 2]) + n2); r3 = q3 * (__uint_as_float(dp[e + 3]) + n3);
+    }
+#endif
+    dsk[(e >> 1) + 0] = pack_bf16(r0, r1);
+    dsk[(e >> 1) + 1] = pack_bf16(r2, r3);
   }
 }
 
@@ -221,7 +265,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     mbar_init(&bar_kv, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bar_q_full[i], 1);
-      mbar_init(&bar_pds[i], 2 * kTile);
+      mbar_init(&bar_pds[i], TS2TS_BWD_ELECT ? 8 : 2 * kTile);  // one arrival per compute warp
     }
     mbar_init(&bar_do_full, 1);
     mbar_init(&bar_gd, 1);
@@ -379,7 +423,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     }
   } else if (warp < 8) {
     // ------------------------------------------------------------------ exp / dS warps: thread = (key row, 32 of 64 queries)
+#if TS2TS_BWD_LD2
+    // register pool: 256 x 128 (these warps keep the launch value) + 128 x 168 + 128 x 88 = 512 x 128
+#else
     reg_dec<120>();
+#endif
     const int row = tid & (kTile - 1), half = tid >> 7;
     const int kv = kb * kTile + row;
     const bool kv_valid = kv < P.T;
@@ -387,6 +435,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const int kvcol = kv_valid ? p.mask.col[(size_t)b * P.T + kv] : -1;
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
+    BTRACE_ACC_DECL
     for (int i = 0; i < n && ok; ++i) {
       const int st = i & 1;
       const int entry = list[i];
@@ -404,48 +453,83 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           }
         }
       }
-      if (!(ok = mbar_wait(&bar_q_full[st], (i >> 1) & 1, abort_w, 30))) break;  // lse2 / delta of this tile landed
+      // per 32-query chunk of this thread, uniform over the warp: 0 all allowed, 1 test bits, 2 nothing allowed
+      int mode[2] = {0, 0};
+      uint32_t bw2[2] = {0xffffffffu, 0xffffffffu};
+      if (masked) {
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          bw2[s] = s == 0 ? (half == 0 ? bits[0] : bits[1]) : (half == 0 ? bits[2] : bits[3]);
+          mode[s] = __all_sync(0xffffffffu, bw2[s] == 0u) ? 2 : (__all_sync(0xffffffffu, bw2[s] == 0xffffffffu) ? 0 : 1);
+        }
+      }
+      if (masked) BTRACE_ACC(0); else BTRACE_ACC(1);
+      if (!(ok = mbar_wait(&bar_q_full[st], (i >> 1) & 1, abort_w, 30))) break;  // -lse2 / -delta of this tile landed
       // ---- phase 1: exponentials, as soon as S^T is complete
       if (!(ok = mbar_wait(&bar_s, i & 1, abort_w, 35))) break;
       tc_fence_after();
+      BTRACE_ACC(2);
       if (tid == 0) TRACE(1, i, 0);
       uint32_t pk[2][16];
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const uint32_t col = lane_base + 64 * s + 32 * half;
-        const uint32_t bw = s == 0 ? (half == 0 ? bits[0] : bits[1]) : (half == 0 ? bits[2] : bits[3]);
-        uint32_t sv[32];
-        tmem_ld32(tST + col, sv);
+      {
+        uint32_t sv[2][32];
+#if TS2TS_BWD_LD2
+        tmem_ld32(tST + lane_base + 32 * half, sv[0]);
+        tmem_ld32(tST + lane_base + 64 + 32 * half, sv[1]);
         tmem_ld_wait();
-        if (tid == 0) TRACE(1, i, s == 0 ? 4 : 6);
-        p_chunk(sv, s_lse2[st] + s * kSubQ + 32 * half, bw, masked, p.scale_log2, pk[s]);
-        if (tid == 0 && s == 0) TRACE(1, i, 5);
-        tmem_st16(tST + col, pk[s]);
+#endif
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+#if !TS2TS_BWD_LD2
+          tmem_ld32(tST + lane_base + 64 * s + 32 * half, sv[s]);
+          tmem_ld_wait();
+#endif
+          p_chunk(sv[s], s_lse2[st] + s * kSubQ + 32 * half, bw2[s], mode[s], p.scale_log2, pk[s]);
+          tmem_st16(tST + lane_base + 64 * s + 32 * half, pk[s]);
+        }
       }
       if (tid == 0) TRACE(1, i, 1);
+      BTRACE_ACC(3);
       // ---- phase 2: dS^T, once dP^T is complete
       if (!(ok = mbar_wait(&bar_st, i & 1, abort_w, 31))) break;
       tc_fence_after();
+      BTRACE_ACC(4);
       if (tid == 0) TRACE(1, i, 2);
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        const uint32_t col = lane_base + 64 * s + 32 * half;
-        uint32_t dp[32], dsk[16];
-        tmem_ld32(tDPT + col, dp);
+      {
+        uint32_t dp[2][32];
+#if TS2TS_BWD_LD2
+        tmem_ld32(tDPT + lane_base + 32 * half, dp[0]);
+        tmem_ld32(tDPT + lane_base + 64 + 32 * half, dp[1]);
         tmem_ld_wait();
-        ds_chunk(pk[s], dp, s_delta[st] + s * kSubQ + 32 * half, dsk);
-        tmem_st16(tST + col + 16, dsk);
-        // dS^T row `row`, queries [64 s + 32 half, +32): four 16-byte chunks of the 128-byte row of half s
-        uint8_t* ds_row = sDS + s * 16384;
+#endif
 #pragma unroll
-        for (int g = 0; g < 4; ++g)
-          *reinterpret_cast<uint4*>(ds_row + sw128_offset(row, 4 * half + g)) = make_uint4(dsk[g * 4 + 0], dsk[g * 4 + 1], dsk[g * 4 + 2], dsk[g * 4 + 3]);
-        tmem_st_wait();
-        fence_async_smem();
-        tc_fence_before();
-        mbar_arrive(&bar_pds[s]);
-        if (tid == 0) TRACE(1, i, 3 + 4 * s);
+        for (int s = 0; s < 2; ++s) {
+          const uint32_t col = lane_base + 64 * s + 32 * half;
+#if !TS2TS_BWD_LD2
+          tmem_ld32(tDPT + col, dp[s]);
+          tmem_ld_wait();
+#endif
+          uint32_t dsk[16];
+          ds_chunk(pk[s], dp[s], s_delta[st] + s * kSubQ + 32 * half, mode[s], dsk);
+          tmem_st16(tST + col + 16, dsk);
+          // dS^T row `row`, queries [64 s + 32 half, +32): four 16-byte chunks of the 128-byte row of half s
+          uint8_t* ds_row = sDS + s * 16384;
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(ds_row + sw128_offset(row, 4 * half + g)) = make_uint4(dsk[g * 4 + 0], dsk[g * 4 + 1], dsk[g * 4 + 2], dsk[g * 4 + 3]);
+          tmem_st_wait();
+          fence_async_smem();
+          tc_fence_before();
+#if TS2TS_BWD_ELECT
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bar_pds[s]);
+#else
+          mbar_arrive(&bar_pds[s]);
+#endif
+          if (tid == 0) TRACE(1, i, 3 + 4 * s);
+        }
       }
+      BTRACE_ACC(5);
     }
     // ---- epilogue: dV (query-half 0 threads) and scale * dK (half 1) -> bf16 -> swizzled smem -> TMA stores.
     //      dV goes through the Q stage the last tile did not use, dK through the dO buffer (its last readers, the
@@ -486,6 +570,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
       tma_store_commit();
       tma_store_wait_all();
     }
+    BTRACE_ACC(6);
+    if ((tid & 127) == 0) BTRACE_ACC_DUMP();
   } else {
     // ------------------------------------------------------------------ dQ reduction warps 8-11, thread = head-dim lane
     reg_inc<168>();
@@ -544,7 +630,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   if (warp == 13) tmem_dealloc(tmem, 512);
 }
 
-// One warp per (b, h, t): delta and lse2.  Rows t >= T of the padded arrays get lse2 = +inf (P = 0) and delta = 0.
+// One warp per (b, h, t): the negated statistics -delta and -lse2.  Rows t >= T of the padded arrays get
+// -lse2 = -inf (P = 0) and delta = 0.
 template <int D>
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* out, const __nv_bfloat16* dout, const float* lse,
                                                        int64_t o_sb, int64_t o_sh, int64_t o_st, int64_t d_sb, int64_t d_sh,
@@ -555,7 +642,7 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* out,
   const int t = (int)(row % Tp);
   const int64_t bh = row / Tp;
   const int h = (int)(bh % H), b = (int)(bh / H);
-  float acc = 0.f, l2 = CUDART_INF_F;
+  float acc = 0.f, l2 = CUDART_INF_F;  // stored negated below: -lse2 (so -inf where P must be 0) and -delta
   if (t < T) {
     const __nv_bfloat16* o = out + b * o_sb + h * o_sh + (int64_t)t * o_st;
     const __nv_bfloat16* d = dout + b * d_sb + h * d_sh + (int64_t)t * d_st;
@@ -572,8 +659,8 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16* out,
     l2 = (l == -CUDART_INF_F) ? CUDART_INF_F : l * 1.4426950408889634f;
   }
   if (lane == 0) {
-    lse2[row] = l2;
-    delta[row] = acc;
+    lse2[row] = -l2;
+    delta[row] = -acc;
   }
 }
 
@@ -640,13 +727,7 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   for (int i = 0; i < 3; ++i) { p.dk_s[i] = sdk[i]; p.dv_s[i] = sdv[i]; }
   p.H = H; p.Tp = Tp; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-#ifdef TS2TS_TRACE
-  static long long* trace_buf = nullptr;
-  if (!trace_buf) cudaMalloc(&trace_buf, 6 * 64 * 8 * sizeof(long long));
-  cudaMemsetAsync(trace_buf, 0, 6 * 64 * 8 * sizeof(long long), stream);
-  p.trace = trace_buf;
-  p.trace_block = getenv("TS2TS_TRACE_BLOCK") ? (unsigned)atoi(getenv("TS2TS_TRACE_BLOCK")) : 0u;
-#endif
+  BTRACE_ATTACH(p, stream);
   {
     ProfileScope timed(1, stream);
     attn_bwd_kernel<D><<<(unsigned)B * H * P.NB, kBwdThreads, BwdSmem<D>::kBytes, stream>>>(mq, mk, mv, mdo, mdk, mdv, mdq, p);
@@ -654,23 +735,7 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   const int64_t n8 = (int64_t)B * H * T * (D / 8);
   dq_convert_kernel<D><<<(unsigned)((n8 + 255) / 256), 256, 0, stream>>>(dq_acc, static_cast<__nv_bfloat16*>(dq), sdq[0], sdq[1],
                                                                          sdq[2], B, H, T, Tp);
-#ifdef TS2TS_TRACE
-  {
-    static long long host[6 * 64 * 8];
-    cudaStreamSynchronize(stream);
-    cudaMemcpy(host, trace_buf, sizeof(host), cudaMemcpyDeviceToHost);
-    FILE* f = fopen(getenv("TS2TS_TRACE_FILE") ? getenv("TS2TS_TRACE_FILE") : "trace.txt", "w");
-    if (f) {
-      for (int r = 0; r < 6; ++r)
-        for (int u = 0; u < 64; ++u) {
-          fprintf(f, "%d %d", r, u);
-          for (int e = 0; e < 8; ++e) fprintf(f, " %lld", host[(r * 64 + u) * 8 + e]);
-          fprintf(f, "\n");
-        }
-      fclose(f);
-    }
-  }
-#endif
+  BTRACE_DUMP(stream);
   return cudaGetLastError() == cudaSuccess ? 0 : -121;
 }
 
