@@ -61,6 +61,7 @@ struct BwdParams {
 
 constexpr int kBwdThreads = 512;  // warps 0-7 exp/dS, 8-11 dQ reduction, 12 TMA producer, 13 MMA issuer, 14-15 idle
 constexpr int kSubQ = 64;         // query columns per compute half
+constexpr int kRunSlotsB = 4;     // runs of a partial query tile that the producer copies to shared memory
 #ifndef TS2TS_BWD_X2
 #define TS2TS_BWD_X2 1
 #endif
@@ -81,7 +82,7 @@ struct BwdSmem {
   // alignment slack.  The kernel declares no static shared memory, so the dynamic region normally starts 1024-byte
   // aligned and the slack stays unused; if it ever does not fit, the kernel reports status 2900 instead of running.
   static constexpr int kTiles = 5 * kTileBytes + kDsBytes + kStageBytes;
-  static constexpr int kSmall = 4 * kTile * 4 + 16 * 8 + 16;
+  static constexpr int kSmall = 4 * kTile * 4 + 16 * 8 + 16 + 2 * kRunSlotsB * 16 + 16;  // statistics, barriers, flags, staged runs
   static constexpr int kSlack = 512;
   static constexpr int kBytes = kTiles + kSmall + kSlack;
   // tensor-memory columns: dV, dK accumulators, S^T (later P^T / dS^T), dP^T (later dQ^T)
@@ -91,29 +92,49 @@ struct BwdSmem {
 template <uint32_t N> __device__ __forceinline__ void reg_inc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
 template <uint32_t N> __device__ __forceinline__ void reg_dec() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
 
-// 128-bit mask of the query rows of tile `qb` that may read key (doc, column class), before causality.
-__device__ __forceinline__ void allowed_rows(const PlanView& P, const MaskArgs& M, int b, int qb, int kvdoc, int kvcol,
-                                             uint32_t (&bits)[4]) {
+// What a backward thread knows about its key: document, column class, and how it looks up "may row class r read my
+// column class": 0 = never (no links, or the key has no class), 1 = words of the transposed table kept in registers
+// (R <= 256), 2 = words of the transposed table read from global memory, 3 = the untransposed table (no transposed
+// one was built).
+struct KeyCtx {
+  int kvdoc, kvcol, mode;
+  unsigned long long lt0, lt1, lt2, lt3;
+  const unsigned long long* lt_row;
+  const int64_t* link_col;  // &link[b][0][kvcol >> 6]
+};
+__device__ __forceinline__ bool row_class_allowed(const KeyCtx& k, const MaskArgs& M, int row) {
+  if (k.mode == 0 || row < 0 || row >= M.R) return false;
+  unsigned long long w;
+  if (k.mode == 1) {
+    const int wi = row >> 6;
+    w = wi == 0 ? k.lt0 : wi == 1 ? k.lt1 : wi == 2 ? k.lt2 : k.lt3;
+    return (w >> (row & 63)) & 1ull;
+  }
+  if (k.mode == 2) return (__ldg(k.lt_row + (row >> 6)) >> (row & 63)) & 1ull;
+  return (static_cast<unsigned long long>(__ldg(k.link_col + (size_t)row * M.W)) >> (k.kvcol & 63)) & 1ull;
+}
+// 128-bit mask of the query rows of tile `qb` that may read this thread's key, before causality.  The first
+// kRunSlotsB runs come from shared memory (`staged`), further ones from the plan in global memory.
+__device__ __forceinline__ void allowed_rows(const PlanView& P, const MaskArgs& M, int b, int qb, const KeyCtx& k,
+                                             const int4* staged, int n, uint32_t (&bits)[4]) {
   bits[0] = bits[1] = bits[2] = bits[3] = 0u;
-  const int n = P.run_cnt[(size_t)b * P.NB + qb];
   const Run* runs = P.runs + ((size_t)b * P.NB + qb) * kTile;
   const int n_valid = min(kTile, P.T - qb * kTile);
-  const bool col_ok = M.link != nullptr && kvcol >= 0 && kvcol < 64 * M.W;
-  const int64_t* link_b = col_ok ? M.link + (size_t)b * M.R * M.W + (kvcol >> 6) : nullptr;
+  auto get_run = [&](int r) { return r < kRunSlotsB ? staged[r] : __ldg(reinterpret_cast<const int4*>(runs + r)); };
+  int4 cur = n > 0 ? get_run(0) : make_int4(0, 0, 0, 0);
+  uint32_t lo[4];
+  prefix_mask(cur.x, lo);
   for (int r = 0; r < n; ++r) {
-    const int4 raw = __ldg(reinterpret_cast<const int4*>(runs + r));
-    const int start = raw.x, doc = raw.y, row = raw.z;
-    const int end = (r + 1 < n) ? __ldg(&runs[r + 1].start) : n_valid;
-    bool ok = doc == kvdoc;
-    if (!ok && col_ok && row >= 0 && row < M.R)
-      ok = (static_cast<unsigned long long>(__ldg(link_b + (size_t)row * M.W)) >> (kvcol & 63)) & 1ull;
-    if (ok) {
+    const int4 nx = r + 1 < n ? get_run(r + 1) : make_int4(n_valid, 0, 0, 0);
+    uint32_t hi[4];
+    prefix_mask(nx.x, hi);  // the run covers rows [cur.x, nx.x)
+    if (cur.y == k.kvdoc || row_class_allowed(k, M, cur.z)) {
 #pragma unroll
-      for (int w = 0; w < 4; ++w) {
-        const int lo = max(start - 32 * w, 0), hi = min(end - 32 * w, 32);
-        if (hi > lo) bits[w] |= (hi - lo == 32 ? 0xffffffffu : ((1u << (hi - lo)) - 1u)) << lo;
-      }
+      for (int w = 0; w < 4; ++w) bits[w] |= hi[w] & ~lo[w];
     }
+#pragma unroll
+    for (int w = 0; w < 4; ++w) lo[w] = hi[w];
+    cur = nx;
   }
 }
 
@@ -224,6 +245,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_ptr = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars + 16) + 4);
   int* abort_w = const_cast<int*>(abort_ptr);
+  int4* s_runs = reinterpret_cast<int4*>(bars + 18);                  // [2 stages][kRunSlotsB] first runs of a partial query tile
+  int* s_nruns = reinterpret_cast<int*>(s_runs + 2 * kRunSlotsB);     // [2] its number of runs
   {  // uniform across the grid: refuse a plan that was not built for this (B, T), or a misplaced shared-memory window
     int bad = 0;
     const int32_t* stw = p.plan.status;
@@ -300,8 +323,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         tma_load_4d(sV + s * 16384, &mapV, &bar_kv, s * 64, kb * kTile, h, b);
       }
       auto load_q = [&](int i) {  // Q tile and row statistics of tile i into stage i & 1
-        const int qb = list[i] & ~kFullBit;
+        const int entry = list[i];
+        const int qb = min(entry & ~kFullBit, NB - 1);
         const int st = i & 1;
+        if (!(entry & kFullBit)) {
+          // partial tile: its first runs travel with the stage (the arrive below publishes these plain stores)
+          const size_t tq = (size_t)b * NB + qb;
+          const int4* src = reinterpret_cast<const int4*>(P.runs + tq * kTile);
+          const int4 r0 = __ldg(src), r1 = __ldg(src + 1), r2 = __ldg(src + 2), r3 = __ldg(src + 3);
+          s_nruns[st] = min(max(__ldg(&P.run_cnt[tq]), 0), kTile);
+          s_runs[st * kRunSlotsB + 0] = r0; s_runs[st * kRunSlotsB + 1] = r1;
+          s_runs[st * kRunSlotsB + 2] = r2; s_runs[st * kRunSlotsB + 3] = r3;
+        }
         mbar_expect_tx(&bar_q_full[st], Cfg::kTileBytes + 2 * kTile * 4);
         for (int s = 0; s < Cfg::kSub; ++s)
           tma_load_4d(sQ + st * Cfg::kTileBytes + s * 16384, &mapQ, &bar_q_full[st], s * 64, qb * kTile, h, b);
@@ -431,19 +464,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     const int row = tid & (kTile - 1), half = tid >> 7;
     const int kv = kb * kTile + row;
     const bool kv_valid = kv < P.T;
-    const int kvdoc = kv_valid ? p.mask.doc[(size_t)b * P.T + kv] : INT32_MIN;
-    const int kvcol = kv_valid ? p.mask.col[(size_t)b * P.T + kv] : -1;
+    KeyCtx key;
+    key.kvdoc = kv_valid ? p.mask.doc[(size_t)b * P.T + kv] : INT32_MIN;
+    key.kvcol = kv_valid ? p.mask.col[(size_t)b * P.T + kv] : -1;
+    key.mode = 0;
+    key.lt0 = key.lt1 = key.lt2 = key.lt3 = 0ull;
+    key.lt_row = nullptr;
+    key.link_col = nullptr;
+    if (p.mask.link != nullptr && key.kvcol >= 0 && key.kvcol < 64 * p.mask.W) {
+      const int t_rows = P.status[kLinkTRows];
+      if (t_rows == p.mask.R && key.kvcol < kLinkTMaxCols) {
+        key.lt_row = P.link_t + ((size_t)b * kLinkTMaxCols + key.kvcol) * kLinkTWords;
+        if (t_rows <= 256) {
+          key.mode = 1;
+          key.lt0 = __ldg(key.lt_row);
+          if (t_rows > 64) key.lt1 = __ldg(key.lt_row + 1);
+          if (t_rows > 128) key.lt2 = __ldg(key.lt_row + 2);
+          if (t_rows > 192) key.lt3 = __ldg(key.lt_row + 3);
+        } else {
+          key.mode = 2;
+        }
+      } else {
+        key.mode = 3;
+        key.link_col = p.mask.link + (size_t)b * p.mask.R * p.mask.W + (key.kvcol >> 6);
+      }
+    }
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     bool ok = true;
     BTRACE_ACC_DECL
     for (int i = 0; i < n && ok; ++i) {
       const int st = i & 1;
       const int entry = list[i];
-      const int qb = entry & ~kFullBit;
+      const int qb = min(entry & ~kFullBit, NB - 1);
       const bool masked = (entry & kFullBit) == 0;
+      if (!(ok = mbar_wait(&bar_q_full[st], (i >> 1) & 1, abort_w, 30))) break;  // Q, -lse2, -delta and staged runs of this tile landed
       uint32_t bits[4] = {0, 0, 0, 0};
       if (masked) {
-        allowed_rows(P, p.mask, b, qb, kvdoc, kvcol, bits);
+        allowed_rows(P, p.mask, b, qb, key, s_runs + st * kRunSlotsB, s_nruns[st], bits);
         if (!kv_valid) bits[0] = bits[1] = bits[2] = bits[3] = 0u;
         if (kb == qb) {  // causal inside the diagonal tile: query rows row..127
 #pragma unroll
@@ -464,7 +521,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
       }
       if (masked) BTRACE_ACC(0); else BTRACE_ACC(1);
-      if (!(ok = mbar_wait(&bar_q_full[st], (i >> 1) & 1, abort_w, 30))) break;  // -lse2 / -delta of this tile landed
       // ---- phase 1: exponentials, as soon as S^T is complete
       if (!(ok = mbar_wait(&bar_s, i & 1, abort_w, 35))) break;
       tc_fence_after();

@@ -146,10 +146,22 @@ __global__ void __launch_bounds__(256) order_kernel(PlanView P) {
   order[rank] = i;
 }
 
-__global__ void stamp_kernel(PlanView P) {
+// One thread per (word, column class, b): gathers 64 row classes' bits for one column class.
+__global__ void __launch_bounds__(128) link_transpose_kernel(PlanView P, MaskArgs M) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x, w = blockIdx.y, b = blockIdx.z;
+  if (c >= 64 * M.W) return;
+  const int64_t* link_b = M.link + (size_t)b * M.R * M.W;
+  unsigned long long out = 0ull;
+  for (int r = 64 * w; r < min(64 * w + 64, M.R); ++r)
+    out |= ((static_cast<unsigned long long>(link_b[(size_t)r * M.W + (c >> 6)]) >> (c & 63)) & 1ull) << (r - 64 * w);
+  P.link_t[((size_t)b * kLinkTMaxCols + c) * kLinkTWords + w] = out;
+}
+
+__global__ void stamp_kernel(PlanView P, int link_t_rows) {
   P.status[kStampMagic] = kPlanMagic;
   P.status[kStampB] = P.B;
   P.status[kStampT] = P.T;
+  P.status[kLinkTRows] = link_t_rows;
 }
 
 // Host entry: fills the plan; optional BlockMask-shaped outputs may be null.
@@ -164,7 +176,12 @@ cudaError_t launch_block_map(PlanView P, MaskArgs M, uint8_t* state_out, int32_t
   lists_kernel<<<dim3((P.NB + 3) / 4, P.B), 128, 0, stream>>>(P, 1, q_cnt, q_idx, full_q_cnt, full_q_idx);
   pair_count_kernel<<<dim3(((P.NB + 1) / 2 + 127) / 128, P.B), 128, 0, stream>>>(P);
   order_kernel<<<dim3((P.NB + 255) / 256, P.B, 3), 256, 0, stream>>>(P);
-  stamp_kernel<<<1, 1, 0, stream>>>(P);
+  int link_t_rows = 0;
+  if (M.link != nullptr && M.R > 0 && M.R <= kLinkTMaxRows && 64 * M.W <= kLinkTMaxCols) {
+    link_t_rows = M.R;
+    link_transpose_kernel<<<dim3((64 * M.W + 127) / 128, (M.R + 63) / 64, P.B), 128, 0, stream>>>(P, M);
+  }
+  stamp_kernel<<<1, 1, 0, stream>>>(P, link_t_rows);
   if (state_out)
     cudaMemcpyAsync(state_out, P.state, (size_t)P.B * P.NB * P.NB, cudaMemcpyDeviceToDevice, stream);
   return cudaGetLastError();

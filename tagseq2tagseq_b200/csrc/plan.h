@@ -29,7 +29,12 @@ constexpr uint32_t kFullBit = 1u << 30;  // set in merged list entries for full 
 enum : int {
   kStatusCode = 0, kStampMagic = 1, kStampB = 2, kStampT = 3,
   kFwdTicket = 8, kFwdDone = 9, kBwdTicket = 10, kBwdDone = 11,
+  kLinkTRows = 12,  // > 0: link_t holds the transposed link bits of this many row classes
 };
+// Transposed link bits: word w of column class c holds, in bit r % 64, whether row class 64 w + r may read c.  A
+// backward thread owns one key, i.e. one column class, and tests many row classes against it; with the transposed
+// table its words are loaded once per CTA.  The table exists when R <= kLinkTMaxRows and 64 W <= kLinkTMaxCols.
+constexpr int kLinkTMaxRows = 1024, kLinkTMaxCols = 1024, kLinkTWords = kLinkTMaxRows / 64;
 constexpr int32_t kPlanMagic = 0x54533254;  // "TS2T"
 
 struct PlanLayout {
@@ -46,6 +51,7 @@ struct PlanLayout {
   size_t bwd_order;   // int32[B,NB]      kv tiles of batch b by descending bwd_cnt
   size_t pair_cnt;    // int32[B,NP]      NP = ceil(NB/2): kv tiles that q tile 2p or 2p+1 reads (forward work items)
   size_t pair_order;  // int32[B,NP]      pairs of batch b by descending pair_cnt
+  size_t link_t;      // uint64[B,kLinkTMaxCols,kLinkTWords]   transposed link bits (see kLinkTRows)
   size_t bytes;
 };
 
@@ -71,6 +77,7 @@ inline PlanLayout plan_layout(int B, int T) {
   const size_t np = (nb + 1) / 2;
   L.pair_cnt = off;   off = plan_align(off + b * np * sizeof(int32_t));
   L.pair_order = off; off = plan_align(off + b * np * sizeof(int32_t));
+  L.link_t = off;     off = plan_align(off + b * kLinkTMaxCols * kLinkTWords * sizeof(uint64_t));
   L.bytes = off;
   return L;
 }
@@ -90,6 +97,7 @@ struct PlanView {
   int32_t* bwd_order;
   int32_t* pair_cnt;
   int32_t* pair_order;
+  unsigned long long* link_t;
 };
 
 inline PlanView plan_view(void* base, int B, int T) {
@@ -109,6 +117,7 @@ inline PlanView plan_view(void* base, int B, int T) {
   v.bwd_order = reinterpret_cast<int32_t*>(p + L.bwd_order);
   v.pair_cnt = reinterpret_cast<int32_t*>(p + L.pair_cnt);
   v.pair_order = reinterpret_cast<int32_t*>(p + L.pair_order);
+  v.link_t = reinterpret_cast<unsigned long long*>(p + L.link_t);
   return v;
 }
 

@@ -279,6 +279,16 @@ __device__ __forceinline__ int4 ld_nc_v4_here(const void* ptr) {
 }
 
 // ----------------------------------------------------------------------------- misc
+// 128-bit mask whose low x bits are set (0 <= x <= 128), as four words.  shl.b32 clamps shift amounts above 31, so a
+// full word comes out as (1 << 32) - 1 = 0 - 1.
+__device__ __forceinline__ void prefix_mask(int x, uint32_t (&m)[4]) {
+#pragma unroll
+  for (int w = 0; w < 4; ++w) {
+    uint32_t v;
+    asm("shl.b32 %0, 1, %1;" : "=r"(v) : "r"(static_cast<uint32_t>(max(x - 32 * w, 0))));
+    m[w] = v - 1u;
+  }
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
