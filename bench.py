@@ -8,8 +8,9 @@ three masks (doc_causal, cross_doc_link with p=0.05 and p=0.3) on seeded synthet
 5 % of documents of 4k-8k tokens).  One step = for each mask: pre-pass, forward, backward.  The metric counts
 only unmasked FLOPs: 14 * D * H * N with N the exact number of allowed (q, kv) pairs.
 
-Prints ONE JSON line on rank 0.  Under torchrun every rank runs its own packs (seed + 1000 * rank); there is no
-collective on this path, so the multi-GPU number is the weak-scaling aggregate over independent replicas.
+Prints ONE JSON line on rank 0.  Under torchrun every rank runs a replica of the same masks on its own q, k, v, dO
+(weak scaling: exactly the same work per GPU at every N); there is no collective on this path, so the multi-GPU
+number is the aggregate over independent replicas, timed as the max over ranks.
 """
 from __future__ import annotations
 
@@ -33,6 +34,21 @@ MASKS = ["doc_causal", "link_p05", "link_p30"]
 SEED = 1003
 WORKLOAD = "attn_fwd_bwd_32k_mask_sweep"
 METRIC = "masked attn fwd+bwd TFLOP/s (unmasked FLOPs) at 32k"
+
+
+def measured_traffic():
+    """DRAM bytes per launch of the two main kernels as one ncu capture measured them, per (batch x head x token) so that
+    they scale to other sizes of the same kernels.  The capture and the commit it was taken at are recorded in the
+    JSON file beside the ncu summary; None when that file is absent."""
+    path = os.path.join(ROOT, "profiles", "attn_kernels_dram_traffic.json")
+    if not os.path.exists(path):
+        return None
+    with open(path) as f:
+        d = json.load(f)
+    units = float(d["B"] * d["H"] * d["T"])
+    return {"bwd_bytes_per_bht": (d["bwd"]["dram_read_bytes"] + d["bwd"]["dram_write_bytes"]) / units,
+            "fwd_bytes_per_bht": (d["fwd"]["dram_read_bytes"] + d["fwd"]["dram_write_bytes"]) / units,
+            "source": f"ncu capture of {d['workload']} at commit {d['commit']}"}
 
 
 def measured_peaks():
@@ -111,16 +127,16 @@ def make_workload(rank: int, device):
     masks = []
     for mi, name in enumerate(MASKS):
         if WORKLOAD == "attn_fwd_bwd_16k_cross_doc_link":
-            packs = [synth.config2_pack(SEED + 1000 * rank + b) for b in range(B)]
+            packs = [synth.config2_pack(SEED + b) for b in range(B)]
         else:
-            packs = [synth.config3_pack(SEED + 1000 * rank + 10 * mi + b, name) for b in range(B)]
+            packs = [synth.config3_pack(SEED + 10 * mi + b, name) for b in range(B)]
         doc_np, link_np = synth.stack_packs(packs)
         n_pairs = sum(p.unmasked_pairs() for p in packs)
         masks.append({"name": name, "doc": torch.from_numpy(doc_np).to(device),
                       "link": None if link_np is None else torch.from_numpy(link_np).to(device),
                       "doc_host": torch.from_numpy(doc_np).pin_memory(),
                       "link_host": None if link_np is None else torch.from_numpy(link_np).pin_memory(),
-                      "pairs": n_pairs, "density": n_pairs / (B * T * T), "docs": [int(p.lengths.size) for p in packs]})
+                      "pairs": n_pairs, "density": n_pairs / (B * T * T), "docs": [int(p.lengths.size) for p in packs], "packs": packs})
     return masks
 
 
@@ -145,7 +161,8 @@ def run_ours(args, rank, world, device):
             bm = build_block_map(m["doc"], m["link"])
             out, lse = _attn_fwd(q, k, v, m["doc"], m["link"], None, None, bm.plan, scale)
             _attn_bwd(q, k, v, out, do, lse, m["doc"], m["link"], None, None, bm.plan, scale)
-            launches[0] += 5 + 1 + 3  # pre-pass kernels, forward, backward (prep, main, convert)
+            # pre-pass (runs, state, 2 x lists, pair counts, orders, stamp; + transposed links), forward, backward (prep, main, convert)
+            launches[0] += 7 + (1 if m["link"] is not None else 0) + 1 + 3
         return bm
 
     def barrier():
@@ -176,6 +193,9 @@ def run_ours(args, rank, world, device):
     per_mask = []
     fms, bms = ctypes.c_float(0), ctypes.c_float(0)
     for m in masks:
+        bml = build_block_map(m["doc"], m["link"], with_lists=True)
+        m["tiles"] = int((bml.q_cnt.sum() + bml.full_q_cnt.sum()).item())  # non-skipped 128 x 128 tiles
+        del bml
         f_list, b_list, pp_list = [], [], []
         for _ in range(max(3, min(args.steps, 5))):
             pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -186,7 +206,8 @@ def run_ours(args, rank, world, device):
             _attn_bwd(q, k, v, out, do, lse, m["doc"], m["link"], None, None, bm.plan, scale)
             L.ts2ts_profile_last_ms(0, ctypes.byref(fms)); L.ts2ts_profile_last_ms(1, ctypes.byref(bms))
             f_list.append(fms.value); b_list.append(bms.value); pp_list.append(pe0.elapsed_time(pe1))
-        per_mask.append({"mask": m["name"], "density": round(m["density"], 4), "fwd_ms": statistics.mean(f_list),
+        per_mask.append({"mask": m["name"], "density": round(m["density"], 4), "tiles": m["tiles"],
+                         "executed_over_algorithmic": m["tiles"] * 16384.0 / m["pairs"], "fwd_ms": statistics.mean(f_list),
                          "bwd_ms": statistics.mean(b_list), "prepass_ms": statistics.median(pp_list), "fwd_tflops": 4.0 * D * H * m["pairs"] / statistics.mean(f_list) / 1e9,
                          "bwd_tflops": 10.0 * D * H * m["pairs"] / statistics.mean(b_list) / 1e9})
     L.ts2ts_profile_enable(0)
@@ -254,19 +275,33 @@ def run_ours(args, rank, world, device):
     h2d = 4 * tens * len(masks) + mask_bytes
     d2h = (4 * tens + B * H * T * 4) * len(masks)
 
+    ref_mask = ref_format = None
+    if world == 1 and WORKLOAD == "attn_fwd_bwd_32k_mask_sweep":
+        ref_mask = reference_block_mask_time(masks[0]["packs"][0], device)
+        ref_format = reference_format_mask_time(masks[2]["packs"][0], q, k, v, do, device)
+
     train = None
     if WORKLOAD == "attn_fwd_bwd_32k_mask_sweep" and not args.no_train:
         del hq, hk, hv, hdo, h_out, h_dq, h_dk, h_dv, slots, q, k, v, do
         torch.cuda.empty_cache()
         train = run_train(args, rank, world, device, "train4", steps=max(2, min(args.steps, 5)), warmup=3)
+        torch.cuda.empty_cache()
+        train5 = run_train(args, rank, world, device, "train5", steps=max(2, min(args.steps, 3)), warmup=3, both_schedules=False)
+        if train is not None and train5 is not None:
+            train["config5"] = train5
 
     t_ms = torch.tensor([ms, e2e_ms], device=device, dtype=torch.float64)
     fl = torch.tensor([total_flops, sum(flops_of(m["pairs"]) for m in masks) * e2e_steps], device=device, dtype=torch.float64)
+    rates = torch.zeros(world, device=device, dtype=torch.float64)  # every rank's own TFLOP/s over its own timed region
+    rates[rank] = total_flops / (ms * 1e-3) / 1e12
     if world > 1:
         torch.distributed.all_reduce(t_ms, op=torch.distributed.ReduceOp.MAX)
         torch.distributed.all_reduce(fl, op=torch.distributed.ReduceOp.SUM)
+        torch.distributed.all_reduce(rates, op=torch.distributed.ReduceOp.SUM)
     if rank != 0:
         return
+    rate_list = sorted(rates.tolist())
+    traffic = measured_traffic()
     value = fl[0].item() / (t_ms[0].item() * 1e-3) / 1e12
     e2e_value = fl[1].item() / (t_ms[1].item() * 1e-3) / 1e12
     line = {
@@ -274,29 +309,121 @@ def run_ours(args, rank, world, device):
         "ms_per_step": t_ms[0].item() / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": WORKLOAD, "B": B, "T": T, "H": H, "head_dim": D, "masks": MASKS,
+                   "replicas": "every rank runs the same masks on its own q,k,v,dO (equal work per GPU)",
                    "doc_lengths": ("lognormal median 150 sigma 1.0 clip [16,4096], 5% uniform [4096,8192]" if T == 32768 else
                                    "lognormal median 200 sigma 1.0 clip [32,2048]"),
                    "l2": "inputs_exceed_l2 (q,k,v,dO = 1.07 GB per call)", "per_mask": per_mask,
                    "step": "per mask: block-map pre-pass + forward + backward", "seed": SEED},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps,
+                "ms_per_step": t_ms[1].item() / e2e_steps,
+                # both directions run concurrently with the kernels; each figure is that direction's bytes over the whole region
+                "h2d_gbs_per_gpu": h2d * e2e_steps / (e2e_ms * 1e-3) / 1e9, "d2h_gbs_per_gpu": d2h * e2e_steps / (e2e_ms * 1e-3) / 1e9,
                 "how": "pinned host q,k,v,dout + mask in, out,lse,dq,dk,dv back to pinned host for every call; copies and kernels on three streams"},
+        "per_rank_tflops": {"min": rate_list[0], "median": statistics.median(rate_list), "max": rate_list[-1]},
         "gpu_launches": n_launch,
         "clocks": clocks.result,
         "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel<128>", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": achieved / peak_tf, "peak_kind": peak_kind + " (burst)", "avg_launch_ms": bwd_ms,
                      "algorithmic_flops_per_launch": bwd_flops,
-                     # dram read+write bytes per launch: ncu capture of the 16k case (633.6 MB, profiles/), scaled by B*H*T
-                     "traffic": 633.6e6 * (B * H * T) / (1 * 16 * 16384) if D == 128 else None,
+                     # dram read + write bytes per launch from the recorded ncu capture, scaled by B*H*T to this workload
+                     "traffic": None if traffic is None else traffic["bwd_bytes_per_bht"] * (B * H * T),
+                     "traffic_source": None if traffic is None else traffic["source"],
                      "fwd": {"achieved": sum(4.0 * D * H * m["pairs"] for m in masks) / sum(p["fwd_ms"] for p in per_mask) / 1e9,
-                             "avg_launch_ms": statistics.mean(p["fwd_ms"] for p in per_mask)}},
+                             "frac": sum(4.0 * D * H * m["pairs"] for m in masks) / sum(p["fwd_ms"] for p in per_mask) / 1e9 / peak_tf,
+                             "avg_launch_ms": statistics.mean(p["fwd_ms"] for p in per_mask),
+                             "traffic": None if traffic is None else traffic["fwd_bytes_per_bht"] * (B * H * T)},
+                     # executed = every element of a non-skipped 128 x 128 tile counted, masked or not
+                     "executed_over_algorithmic_flops": sum(m["tiles"] for m in masks) * 16384.0 / sum(m["pairs"] for m in masks)},
     }
     if world == 1:
-        line["cpu_baseline"] = cpu_baseline(steps=1)
+        line["cpu_baseline"] = cpu_baseline(steps=5)
     if train is not None:
         line["train_step"] = train
     if world == 1:
         line["link_scan"] = link_scan_bench(device)
+    if ref_mask is not None:
+        line["block_map_vs_reference"] = ref_mask
+    if ref_format is not None:
+        line["reference_format_mask"] = ref_format
     emit(line)
+
+
+def reference_block_mask_time(pack, device):
+    """The mask build the reference does once per micro-batch, timed beside this package's pre-pass on the same pack:
+    torch's create_block_mask with the reference's doc_causal mask_mod and arguments (B=None, H=None, eager, as in
+    model/graph_traversal/block_mask_creator.py:121-139), which materialises the dense T x T mask on the GPU."""
+    from torch.nn.attention.flex_attention import create_block_mask
+    from tagseq2tagseq_b200.mask_spec import build_block_map
+    doc_np = pack.doc_ids
+    t = int(doc_np.shape[0])
+    document_ids = torch.from_numpy(doc_np).to(device)
+
+    def doc_causal_mod(b, h, q_idx, kv_idx):
+        return (q_idx >= kv_idx) & (document_ids[q_idx] == document_ids[kv_idx])
+
+    def timed(fn, warm, reps):
+        for _ in range(warm):
+            fn()
+        torch.cuda.synchronize(device)
+        out = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize(device)
+            out.append(e0.elapsed_time(e1))
+        return statistics.median(out)
+
+    try:
+        ref_ms = timed(lambda: create_block_mask(doc_causal_mod, B=None, H=None, Q_LEN=t, KV_LEN=t, device=device), 3, 5)
+    except Exception as exc:  # noqa: BLE001 - a torch-side failure must not cost the whole line
+        return {"unavailable": str(exc).splitlines()[0][:200]}
+    doc1 = document_ids[None].contiguous()
+    ours_ms = timed(lambda: build_block_map(doc1, None), 3, 5)
+    torch.cuda.empty_cache()
+    return {"mask": "doc_causal pack 0, B=1, T=%d" % t, "reference_create_block_mask_ms": ref_ms, "prepass_ms": ours_ms,
+            "how": "3 warm-ups, median of 5, CUDA events; torch.nn.attention.flex_attention.create_block_mask (eager) with the reference's mask_mod"}
+
+
+def reference_format_mask_time(pack, q, k, v, do, device):
+    """Forward / backward on a mask in the reference's own grant format: every link of the pack starts in the middle of
+    its source document (link_end_pos), so documents split into several row classes, and at most 256 grants are kept
+    (the reference's largest max_grants).  Built through the host adapter from_reference; same q, k, v, dO (batch 0)."""
+    from types import SimpleNamespace
+    from tagseq2tagseq_b200 import _lib
+    from tagseq2tagseq_b200.attention import _attn_bwd, _attn_fwd
+    from tagseq2tagseq_b200.mask_spec import from_reference, ordered_grants
+    L = _lib.lib()
+    lengths = pack.lengths
+    starts = np.concatenate([[0], np.cumsum(lengths)[:-1]])
+    spans = [SimpleNamespace(doc_id=i, start=int(starts[i]), end=int(starts[i] + lengths[i])) for i in range(len(lengths))]
+    link_to_target = {}
+    for a, b_ in pack.links:
+        pos = int(starts[a] + max(1, lengths[a] // 2))
+        link_to_target.setdefault(pos, []).append(int(b_))
+    t = int(pack.doc_ids.shape[0])
+    spec = from_reference(spans, link_to_target, t, max_grants_cap=256, device=device)
+    grants = ordered_grants(t, spans, link_to_target, 256)
+    pairs = int(sum(int(n) * (int(n) + 1) // 2 for n in lengths))
+    covered = set()
+    for q0, q1, k0, k1 in grants:  # grants may overlap: count every (source rows, target document) block once
+        covered.add((q0, q1, k0, k1))
+    pairs += sum((q1 - q0) * (k1 - k0) for q0, q1, k0, k1 in covered)
+    q1_, k1_, v1_, do1_ = (x[:1] for x in (q, k, v, do))
+    scale = 1.0 / D ** 0.5
+    L.ts2ts_profile_enable(1)
+    fms, bms = ctypes.c_float(0), ctypes.c_float(0)
+    f_list, b_list = [], []
+    for _ in range(4):
+        out, lse = _attn_fwd(q1_, k1_, v1_, spec.doc_ids, spec.link_bits, spec.q_row_ids, spec.kv_col_ids, spec.plan, scale)
+        _attn_bwd(q1_, k1_, v1_, out, do1_, lse, spec.doc_ids, spec.link_bits, spec.q_row_ids, spec.kv_col_ids, spec.plan, scale)
+        L.ts2ts_profile_last_ms(0, ctypes.byref(fms)); L.ts2ts_profile_last_ms(1, ctypes.byref(bms))
+        f_list.append(fms.value); b_list.append(bms.value)
+    L.ts2ts_profile_enable(0)
+    f_ms, b_ms = statistics.median(f_list[1:]), statistics.median(b_list[1:])
+    return {"mask": "link_p30 pack 0 as reference grants from mid-document link positions, cap 256", "grants": len(grants),
+            "row_classes": int(spec.link_bits.shape[1]), "B": 1, "fwd_ms": f_ms, "bwd_ms": b_ms,
+            "fwd_tflops": 4.0 * D * H * pairs / f_ms / 1e9, "bwd_tflops": 10.0 * D * H * pairs / b_ms / 1e9,
+            "note": "overlapping grants are counted once per distinct (row range, target) block; an upper bound when blocks overlap"}
 
 
 def link_scan_bench(device):
@@ -363,58 +490,101 @@ def link_scan_bench(device):
     return out
 
 
-def run_train(args, rank, world, device, which: str, steps: int, warmup: int):
-    """Training step of the 12-layer (train4) or 24-layer (train5) decoder LM, one packed sequence per rank, DDP."""
+def run_train(args, rank, world, device, which: str, steps: int, warmup: int, both_schedules: bool = True):
+    """Training step of the 12-layer (train4) or 24-layer (train5) decoder LM, one packed sequence per rank, DDP.
+
+    Packs come from a pool of world * n_packs seeded packs that every rank derives identically.  Two schedules are
+    timed: the density-aware one (packs of similar attention cost share a step; the cost of a pack is its number of
+    non-skipped tiles, read from the block-map pre-pass) and plain seed order, which is what the reference does."""
     from tagseq2tagseq_b200 import synth
     from tagseq2tagseq_b200.mask_spec import MaskSpec
-    from tagseq2tagseq_b200.replicas import aggregate, rank_seed
+    from tagseq2tagseq_b200.replicas import aggregate, rank_seed, schedule_packs, tile_cost
     from tagseq2tagseq_b200.train_step import TrainStep, config4, config5, train_flops_per_step
     cfg, t_len, base = (config4(), 16384, 1004) if which == "train4" else (config5(), 32768, 1005)
     ts = TrainStep(cfg, device, world)
-    n_packs = 4  # steps in the pool; every rank derives the same pool of world * n_packs packs from the seeds
-    from tagseq2tagseq_b200.replicas import schedule_packs
+    n_packs = 4  # steps in the pool
     make = (lambda sd: synth.config2_pack(sd)) if which == "train4" else (lambda sd: synth.config5_pack(sd))
     pool = [make(rank_seed(base, r, i)) for i in range(n_packs) for r in range(world)]
-    if args.no_balance:
-        mine = [i * world + rank for i in range(n_packs)]
-    else:  # packs of similar attention cost share a step, so that no rank waits long for the slowest one
-        sched = schedule_packs([float(pk.unmasked_pairs()) for pk in pool], world)
-        mine = [sched[i][rank] for i in range(n_packs)]
-    packs = [pool[i] for i in mine]
-    g = torch.Generator().manual_seed(rank_seed(base, rank))
-    batches = []
-    for pk in packs:
+
+    def to_spec(pk):
         doc_np, link_np = synth.stack_packs([pk])
-        spec = MaskSpec(doc_ids=torch.from_numpy(doc_np).to(device), link_bits=torch.from_numpy(link_np).to(device))
-        tokens = torch.randint(0, cfg.vocab, (1, t_len + 1), generator=g).to(device)
-        batches.append((tokens, spec, pk.unmasked_pairs()))
-    for i in range(warmup):
-        tok, spec, _ = batches[i % n_packs]
-        spec._block_map = None
-        loss = ts.step(tok, spec)
-    if world > 1:
-        torch.distributed.barrier()
-    torch.cuda.synchronize(device)
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    flops = 0.0
-    for i in range(steps):
-        tok, spec, pairs = batches[i % n_packs]
-        spec._block_map = None  # the pre-pass is part of every step, as in the reference (one mask build per micro-batch)
-        loss = ts.step(tok, spec)
-        flops += train_flops_per_step(cfg, t_len, pairs)
-    ev1.record()
-    if world > 1:
-        torch.distributed.barrier()
-    torch.cuda.synchronize(device)
-    (ms,), (tot_flops, tot_tokens) = aggregate([ev0.elapsed_time(ev1)], [flops, float(t_len * steps)], device)
+        return MaskSpec(doc_ids=torch.from_numpy(doc_np).to(device), link_bits=torch.from_numpy(link_np).to(device))
+
+    costs = None
+    if world > 1 and not args.no_balance:
+        costs = []
+        for pk in pool:
+            sp = to_spec(pk)
+            costs.append(float(tile_cost(sp.doc_ids, sp.link_bits)))
     peak_tf, _, kind = measured_peaks()
-    return {"metric": "train tokens/s", "value": tot_tokens / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms / steps, "steps": steps,
-            "model": f"{cfg.n_layers}L d{cfg.d_model} {cfg.n_heads}h hd{cfg.head_dim} swiglu{cfg.mlp_hidden} V{cfg.vocab}",
-            "seq_len": t_len, "global_batch_tokens": t_len * world, "parallelism": f"ddp{world}", "pack_schedule": "seed order" if args.no_balance else "density-aware (similar-cost packs share a step)",
-            "optimizer": "fused AdamW (fp32 params, bf16 autocast)",
-            "model_tflops": tot_flops / (ms * 1e-3) / 1e12, "frac_of_peak": tot_flops / (ms * 1e-3) / 1e12 / (peak_tf * world),
-            "peak_kind": kind, "loss": float(loss)}
+
+    def measure(schedule_name):
+        if schedule_name == "seed order" or costs is None:
+            mine = [i * world + rank for i in range(n_packs)]
+        else:
+            sched = schedule_packs(costs, world)
+            mine = [sched[i][rank] for i in range(n_packs)]
+        g = torch.Generator().manual_seed(rank_seed(base, rank))
+        batches = []
+        for i in mine:
+            batches.append((torch.randint(0, cfg.vocab, (1, t_len + 1), generator=g).to(device), to_spec(pool[i]), pool[i].unmasked_pairs()))
+        for i in range(warmup):
+            tok, spec, _ = batches[i % n_packs]
+            spec._block_map = None
+            loss = ts.step(tok, spec)
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        flops = 0.0
+        for i in range(steps):
+            tok, spec, pairs = batches[i % n_packs]
+            spec._block_map = None  # the pre-pass is part of every step, as in the reference (one mask build per micro-batch)
+            loss = ts.step(tok, spec)
+            flops += train_flops_per_step(cfg, t_len, pairs)
+        ev1.record()
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize(device)
+        my_ms = ev0.elapsed_time(ev1)
+        (ms,), (tot_flops, tot_tokens) = aggregate([my_ms], [flops, float(t_len * steps)], device)
+        res = {"value": tot_tokens / (ms * 1e-3), "ms_per_step": ms / steps,
+               "model_tflops": tot_flops / (ms * 1e-3) / 1e12, "frac_of_peak": tot_flops / (ms * 1e-3) / 1e12 / (peak_tf * world),
+               "loss": float(loss)}
+        if world > 1:
+            # What the collective and the slowest rank cost: forward + backward of every pack of the schedule with and
+            # without the gradient all-reduce (DDP no_sync), timed per rank without barriers in between.
+            def fb_ms(sync):
+                torch.cuda.synchronize(device)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for tok, spec, _ in batches:
+                    ts.forward_backward(tok, spec, sync=sync)
+                e1.record()
+                torch.cuda.synchronize(device)
+                return e0.elapsed_time(e1) / len(batches)
+            local = fb_ms(False)
+            torch.distributed.barrier()
+            synced = fb_ms(True)
+            v = torch.tensor([local, -local, synced], device=device, dtype=torch.float64)
+            torch.distributed.all_reduce(v, op=torch.distributed.ReduceOp.MAX)
+            res["fwd_bwd_ms_without_allreduce"] = {"max_over_ranks": v[0].item(), "min_over_ranks": -v[1].item()}
+            res["fwd_bwd_ms_with_allreduce_max"] = v[2].item()
+        return res
+
+    first = "seed order" if (args.no_balance or world == 1) else "density-aware (similar-cost packs share a step; cost = non-skipped tiles from the pre-pass)"
+    main = measure(first)
+    out = {"metric": "train tokens/s", "unit": "tokens/s", "steps": steps,
+           "model": f"{cfg.n_layers}L d{cfg.d_model} {cfg.n_heads}h hd{cfg.head_dim} swiglu{cfg.mlp_hidden} V{cfg.vocab}",
+           "seq_len": t_len, "global_batch_tokens": t_len * world, "parallelism": f"ddp{world}", "pack_schedule": first,
+           "optimizer": "fused AdamW (fp32 params, bf16 autocast)",
+           "gradient_allreduce": "none (1 GPU)" if world == 1 else f"NCCL, {'bf16-compressed' if ts.bf16_grads else 'fp32'} buckets, {ts.grad_bytes_per_step / 1e9:.2f} GB per rank per step",
+           "peak_kind": kind}
+    out.update(main)
+    if both_schedules and world > 1 and not args.no_balance:
+        out["seed_order_schedule"] = measure("seed order")
+    return out
 
 
 def cpu_sample():
@@ -433,8 +603,7 @@ def cpu_sample():
 
 
 def reference_mask_and_step():
-    """The reference's own CPU code for this path, when its sources were installed under baseline/_ref
-    (pip --no-deps; they travel with the repository snapshot): dense mask from
+    """The reference's own CPU code for this path, when its sources are present under baseline/_ref: dense mask from
     CrossDocLinkMaskCreator.build_dense_mask_for_visualization (model/graph_traversal/cross_doc_mask.py:371-409),
     attention = fp32 F.scaled_dot_product_attention + autograd (FlexAttention has no CPU backward).
     Returns None when baseline/_ref is absent, so that the oracle port is used instead."""
@@ -493,16 +662,17 @@ def cpu_baseline(steps: int):
     from oracle import attention as oattn
     torch.set_num_threads(os.cpu_count() or 1)
     dense, q, k, v, do, pairs, heads, t = cpu_sample()
-    oattn.forward_backward(q, k, v, dense, do)  # warm-up
+    for _ in range(3):  # warm-ups
+        oattn.forward_backward(q, k, v, dense, do)
     times = []
-    for _ in range(max(1, steps)):
+    for _ in range(max(5, steps)):
         t0 = time.perf_counter()
         oattn.forward_backward(q, k, v, dense, do)
         times.append(time.perf_counter() - t0)
     sec = statistics.median(times)
     return {"value": 14.0 * D * heads * pairs / sec / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
             "sample": f"doc_causal pack, first {t} tokens, {heads} heads, fp32 dense-masked attention fwd+bwd, unmasked FLOPs credited",
-            "sec_per_sample": sec}
+            "sec_per_sample": sec, "timing": f"3 warm-ups, median of {len(times)}"}
 
 
 def run_reference(args, rank, world):

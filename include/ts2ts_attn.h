@@ -101,9 +101,16 @@ int ts2ts_attn_bwd(const void* q, const void* k, const void* v, const void* out,
  * Same arguments and results as ts2ts_attn_bwd, minus the workspace.  Limits and rules:
  *   - the problem must satisfy ts2ts_attn_bwd_workspace_bytes(B,H,T,D) <= ts2ts_attn_bwd_noalloc_max_bytes()
  *     (64 MiB, e.g. H * ceil(T/128)*128 <= 129055 rows at D = 128); larger problems are rejected with -10;
- *   - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
- *     current) and caches it, so make the first call on each device before starting any stream capture;
- *   - the call allocates nothing: no cudaMalloc / cudaFree and no allocating library routine;
+ *   - set-up, once per device at start-up: call ts2ts_attn_bwd_noalloc_max_bytes() with that device current.  It
+ *     looks up the array's device address (cudaGetSymbolAddress) and caches it; with CUDA's lazy module loading
+ *     this is also the moment the module that holds the 64 MiB array is loaded and the array gets its memory, and
+ *     the look-up may synchronise the device.  So make this call BEFORE the rest of the GPU's memory is handed to
+ *     another allocator (afterwards the load can fail with -131) and before any stream capture.  The first
+ *     ts2ts_attn_bwd_noalloc on a device does the same set-up if it was skipped.  The cache is indexed by device
+ *     ordinal: after cudaDeviceReset, or in a second context on the same device, the cached address is stale and
+ *     the process must not use this entry point again;
+ *   - once set up, the call allocates nothing: no cudaMalloc / cudaFree and no allocating library routine, and
+ *     the amount of free device memory is the same before and after it;
  *   - all calls on a device share the one array, which still holds the previous call's values: each call
  *     re-zeroes the accumulator part and rewrites the rest before use, and two calls whose kernels can
  *     overlap on the GPU (different streams without ordering) race -- serialise them. */

@@ -35,8 +35,8 @@ def _check_qkv(q, k, v):
 
 def _rowmajor(t: torch.Tensor) -> torch.Tensor:
     """The kernels need a unit stride in D and 16-byte aligned rows; anything else is copied once."""
-    if t.stride(-1) != 1 or any((s * 2) % 16 for s in t.stride()[:-1]) or t.data_ptr() % 16:
-        return t.contiguous()
+    if t.stride(-1) != 1 or any(s <= 0 or (s * 2) % 16 for s in t.stride()[:-1]) or t.data_ptr() % 16:
+        return t.contiguous()  # also expanded (stride 0) views: the TMA descriptors need positive strides
     return t
 
 
@@ -147,10 +147,7 @@ def flex_attention(query, key, value, score_mod=None, block_mask=None, scale=Non
         raise NotImplementedError("only block_mask / scale / return_lse are used on the reference's path")
     if not isinstance(block_mask, MaskSpec):
         raise TypeError("block_mask must be a MaskSpec from tagseq2tagseq_b200.mask_spec")
-    m = block_mask
-    B = query.shape[0]
-    expand = (lambda t: None if t is None else t.expand(B, *t.shape[1:])) if m.doc_ids.shape[0] == 1 and B > 1 else (lambda t: t)
-    plan = m.plan if m.doc_ids.shape[0] == B else None
-    out, lse = masked_attn(query, key, value, expand(m.doc_ids), expand(m.link_bits), q_row_ids=expand(m.q_row_ids),
-                           kv_col_ids=expand(m.kv_col_ids), scale=scale, plan=plan)
+    m = block_mask.expanded(query.shape[0])  # a one-sequence spec serves every sequence of the batch; its plan is cached
+    out, lse = masked_attn(query, key, value, m.doc_ids, m.link_bits, q_row_ids=m.q_row_ids, kv_col_ids=m.kv_col_ids,
+                           scale=scale, plan=m.plan)
     return (out, lse) if return_lse else out

@@ -16,6 +16,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libts2ts_attn.so")
+SELFTEST_LIB = os.path.join(HERE, "libts2ts_selftest.so")  # test-only: the bounded-wait self-test kernel
 SOURCES = ["api.cu", "block_map.cu", "link_scan.cu", "attn_fwd.cu", "attn_bwd.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v"]
@@ -29,7 +30,7 @@ def _nvcc() -> str:
 
 
 def _stale() -> bool:
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or not os.path.exists(SELFTEST_LIB):
         return True
     t = os.path.getmtime(LIB)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "ts2ts_attn.h")]
@@ -60,6 +61,11 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    cmd = [nvcc, *[f for f in NVCC_FLAGS if f not in ("-Xptxas", "-v")], "-DTS2TS_SPIN_LIMIT=4096u", "-shared",
+           os.path.join(CSRC, "selftest_wait.cu"), "-o", SELFTEST_LIB, "-cudart", "static"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"self-test library failed to build:\n{res.stdout}\n{res.stderr}")
     return LIB
 
 

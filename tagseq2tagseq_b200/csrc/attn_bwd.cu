@@ -758,13 +758,13 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   float* dq_acc = reinterpret_cast<float*>(ws + 2 * plan_align(rows * 4));
   CUtensorMap mq, mk, mv, mdo, mdk, mdv, mdq;
   int r;
-  if ((r = make_tile_map(&mq, q, 2, B, H, T, D, sq[0], sq[1], sq[2], kTile, 64))) return r;
-  if ((r = make_tile_map(&mk, k, 2, B, H, T, D, sk[0], sk[1], sk[2], kTile, 64))) return r;
-  if ((r = make_tile_map(&mv, v, 2, B, H, T, D, sv[0], sv[1], sv[2], kTile, 64))) return r;
-  if ((r = make_tile_map(&mdo, dout, 2, B, H, T, D, sdo[0], sdo[1], sdo[2], kTile, 64))) return r;
-  if ((r = make_tile_map(&mdk, dk, 2, B, H, T, D, sdk[0], sdk[1], sdk[2], kTile, 64))) return r;
-  if ((r = make_tile_map(&mdv, dv, 2, B, H, T, D, sdv[0], sdv[1], sdv[2], kTile, 64))) return r;
-  if ((r = make_tile_map(&mdq, dq_acc, 4, B, H, Tp, D, (int64_t)H * Tp * D, (int64_t)Tp * D, D, 32, 32))) return r;
+  if ((r = cached_tile_map(&mq, q, 2, B, H, T, D, sq[0], sq[1], sq[2], kTile, 64))) return r;
+  if ((r = cached_tile_map(&mk, k, 2, B, H, T, D, sk[0], sk[1], sk[2], kTile, 64))) return r;
+  if ((r = cached_tile_map(&mv, v, 2, B, H, T, D, sv[0], sv[1], sv[2], kTile, 64))) return r;
+  if ((r = cached_tile_map(&mdo, dout, 2, B, H, T, D, sdo[0], sdo[1], sdo[2], kTile, 64))) return r;
+  if ((r = cached_tile_map(&mdk, dk, 2, B, H, T, D, sdk[0], sdk[1], sdk[2], kTile, 64))) return r;
+  if ((r = cached_tile_map(&mdv, dv, 2, B, H, T, D, sdv[0], sdv[1], sdv[2], kTile, 64))) return r;
+  if ((r = cached_tile_map(&mdq, dq_acc, 4, B, H, Tp, D, (int64_t)H * Tp * D, (int64_t)Tp * D, D, 32, 32))) return r;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);

@@ -716,7 +716,7 @@ template <int D>
 static int launch_fwd_t(const void* q, const void* k, const void* v, void* out, float* lse, const int64_t* sq,
                         const int64_t* sk, const int64_t* sv, const int64_t* so, int B, int H, int T, float scale,
                         PlanView P, MaskArgs M, cudaStream_t stream) {
-  const CUtensorMap *mq, *mk, *mv, *mo;
+  CUtensorMap mq, mk, mv, mo;
   int r;
   if ((r = cached_tile_map(&mq, q, 2, B, H, T, D, sq[0], sq[1], sq[2], kTile, 64))) return r;
   if ((r = cached_tile_map(&mk, k, 2, B, H, T, D, sk[0], sk[1], sk[2], kTile, 64))) return r;
@@ -748,7 +748,7 @@ static int launch_fwd_t(const void* q, const void* k, const void* v, void* out, 
   FTRACE_ATTACH(p, stream);
   {
     ProfileScope timed(0, stream);
-    attn_fwd_kernel<D><<<grid, kFwdThreads, FwdSmem<D>::kBytes, stream>>>(*mq, *mk, *mv, *mo, p);
+    attn_fwd_kernel<D><<<grid, kFwdThreads, FwdSmem<D>::kBytes, stream>>>(mq, mk, mv, mo, p);
   }
   FTRACE_DUMP(stream);
   return cudaGetLastError() == cudaSuccess ? 0 : -111;

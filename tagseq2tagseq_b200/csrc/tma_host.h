@@ -51,15 +51,14 @@ inline int make_tile_map(CUtensorMap* out, const void* base, int elem_bytes, int
 
 // The same map through a small per-process cache: a training step calls the attention entry points once per layer
 // with the same few (pointer, shape, strides) combinations, and encoding a map costs a driver call each time.
-// The returned pointer stays valid until kMapCacheSize other maps have been requested; a launch copies the map
-// into its kernel parameters before it returns, so callers use it for one launch only.
+// The map is copied out, so a later request that recycles the cache entry cannot change what a caller holds.
 constexpr int kMapCacheSize = 64;
 struct MapKey {
   const void* base;
   int64_t v[9];
   int dev;
 };
-inline int cached_tile_map(const CUtensorMap** out, const void* base, int elem_bytes, int64_t B, int64_t H, int64_t T, int64_t D,
+inline int cached_tile_map(CUtensorMap* out, const void* base, int elem_bytes, int64_t B, int64_t H, int64_t T, int64_t D,
                            int64_t sb, int64_t sh, int64_t st, int box_rows, int box_cols) {
   struct Entry { MapKey key; CUtensorMap map; bool used; };
   static Entry cache[kMapCacheSize];
@@ -74,7 +73,7 @@ inline int cached_tile_map(const CUtensorMap** out, const void* base, int elem_b
   std::lock_guard<std::mutex> lock(mu);
   for (int i = 0; i < kMapCacheSize; ++i)
     if (cache[i].used && memcmp(&cache[i].key, &key, sizeof(key)) == 0) {
-      *out = &cache[i].map;
+      *out = cache[i].map;
       return 0;
     }
   Entry& e = cache[next];
@@ -85,7 +84,7 @@ inline int cached_tile_map(const CUtensorMap** out, const void* base, int elem_b
   }
   e.key = key;
   e.used = true;
-  *out = &e.map;
+  *out = e.map;
   next = (next + 1) % kMapCacheSize;
   return 0;
 }

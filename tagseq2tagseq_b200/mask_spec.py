@@ -127,6 +127,21 @@ class MaskSpec:
     q_row_ids: Optional[torch.Tensor] = None   # int32 [B,T]
     kv_col_ids: Optional[torch.Tensor] = None  # int32 [B,T]
     _block_map: Optional[BlockMap] = None
+    _expanded: Optional[Dict[int, "MaskSpec"]] = None
+
+    def expanded(self, batch: int) -> "MaskSpec":
+        """This spec repeated over ``batch`` sequences (the reference's B=None BlockMask broadcasts over the batch),
+        with its own block plan; built once per batch size and kept."""
+        if self.doc_ids.shape[0] == batch:
+            return self
+        if self.doc_ids.shape[0] != 1:
+            raise ValueError("only a spec of one sequence can be broadcast over a batch")
+        if self._expanded is None:
+            self._expanded = {}
+        if batch not in self._expanded:
+            rep = lambda t: None if t is None else t.expand(batch, *t.shape[1:]).contiguous()
+            self._expanded[batch] = MaskSpec(rep(self.doc_ids), rep(self.link_bits), rep(self.q_row_ids), rep(self.kv_col_ids))
+        return self._expanded[batch]
 
     @property
     def seq_len(self) -> int:
@@ -289,8 +304,27 @@ class CrossDocLinkMaskCreator:
         return from_reference(doc_spans, link_to_target, seq_len, max_grants_cap=cap, device=tokens.device)
 
 
+def create_causal_block_mask(tokens: torch.Tensor, doc_spans: List[Any], **kwargs) -> MaskSpec:
+    """Plain causal attention over the whole sequence (block_mask_creator.py:143-172): one document id everywhere,
+    so the doc_causal kernels compute it unchanged."""
+    seq_len = tokens.shape[-1]
+    return MaskSpec(doc_ids=torch.zeros((1, seq_len), dtype=torch.int32, device=tokens.device))
+
+
+def _needs_non_causal_kernel(name: str):
+    def creator(tokens: torch.Tensor, doc_spans: List[Any], **kwargs) -> MaskSpec:
+        raise NotImplementedError(
+            f"mask creator '{name}' lets queries read later keys; the CUDA kernels of this package are causal "
+            "(every mask is intersected with q >= kv), so a non-causal forward / backward kernel would be needed")
+    return creator
+
+
 MASK_CREATORS = {
     "doc_causal": create_doc_causal_block_mask,
+    "causal": create_causal_block_mask,
+    # present in the reference's registry (block_mask_creator.py:251-256) but not computable by causal kernels:
+    "full": _needs_non_causal_kernel("full"),
+    "doc_bidirectional": _needs_non_causal_kernel("doc_bidirectional"),
     # 'cross_doc_link' needs a LinkDetector: build CrossDocLinkMaskCreator yourself and wrap it with
     # make_mask_creator_callable_from (same rule as block_mask_creator.py:254-263).
 }

@@ -29,6 +29,15 @@ def aggregate(elapsed_ms: Sequence[float], work: Sequence[float], device=None) -
     return t.tolist(), w.tolist()
 
 
+def tile_cost(doc_ids: torch.Tensor, link_bits=None, q_row_ids=None, kv_col_ids=None) -> int:
+    """Attention cost of one packed sequence as the pre-pass sees it: the number of non-skipped 128 x 128 tiles
+    (partial + full), read back once from the device.  This is what a real data pipeline can know about a pack before
+    it trains on it -- the mask inputs, not the generator's document lengths."""
+    from .mask_spec import build_block_map
+    bm = build_block_map(doc_ids, link_bits, q_row_ids, kv_col_ids, with_lists=True)
+    return int((bm.q_cnt.sum() + bm.full_q_cnt.sum()).item())
+
+
 def schedule_packs(costs: Sequence[float], world: int) -> list:
     """Density-aware pack -> (step, rank) schedule.
 

@@ -11,6 +11,7 @@ Everything except the attention operator is ordinary PyTorch (cuBLAS GEMMs, fuse
 from __future__ import annotations
 
 import math
+from contextlib import nullcontext as _nullcontext
 from dataclasses import dataclass
 from typing import Optional
 
@@ -116,26 +117,50 @@ class DecoderLM(nn.Module):
 
 class TrainStep:
     """One optimizer step on one packed sequence per rank: forward under bf16 autocast, backward (DDP all-reduces
-    the gradients over NCCL in 256 MB buckets, overlapped with the backward), fused AdamW."""
+    the gradients, overlapped with the backward), fused AdamW on fp32 parameters.
 
-    def __init__(self, cfg: LMConfig, device: torch.device, world: int = 1, lr: float = 3e-4, seed: int = 0):
+    DDP settings follow main.py:404-415 (static graph, no unused parameters, 256 MB buckets; the first bucket keeps
+    torch's small default so that the last gradients to be produced start their all-reduce early).  With
+    ``bf16_grads`` the buckets are cast to bf16 for the all-reduce and back (torch's ``bf16_compress_hook``), which
+    halves the bytes on NVLink; the parameters and the optimizer state stay fp32."""
+
+    def __init__(self, cfg: LMConfig, device: torch.device, world: int = 1, lr: float = 3e-4, seed: int = 0,
+                 bf16_grads: bool = True):
         torch.manual_seed(seed)  # identical initial weights on every rank
         self.cfg, self.device, self.world = cfg, device, world
         model = DecoderLM(cfg).to(device)
         self.model = model
+        self.bf16_grads = bool(bf16_grads and world > 1)
         if world > 1:
             self.model = torch.nn.parallel.DistributedDataParallel(
                 model, device_ids=[device.index], static_graph=True, find_unused_parameters=False, bucket_cap_mb=256,
                 gradient_as_bucket_view=True)
+            if self.bf16_grads:
+                from torch.distributed.algorithms.ddp_comm_hooks import default_hooks
+                self.model.register_comm_hook(None, default_hooks.bf16_compress_hook)
         self.opt = torch.optim.AdamW(model.parameters(), lr=lr, betas=(0.9, 0.95), weight_decay=0.1, fused=True)
 
-    def step(self, tokens: torch.Tensor, mask: MaskSpec) -> torch.Tensor:
+    @property
+    def grad_bytes_per_step(self) -> int:
+        """Bytes each rank contributes to the gradient all-reduce of one step."""
+        n = sum(p.numel() for p in self.model.parameters())
+        return n * (2 if self.bf16_grads else 4)
+
+    def forward_backward(self, tokens: torch.Tensor, mask: MaskSpec, sync: bool = True) -> torch.Tensor:
+        """Loss and gradients without the optimizer step.  ``sync=False`` skips the gradient all-reduce (DDP's
+        ``no_sync``): the difference between the two is what the collective costs this rank."""
         self.opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            loss = self.model(tokens, mask)
-        loss.backward()
-        self.opt.step()
+        ctx = self.model.no_sync() if (not sync and self.world > 1) else _nullcontext()
+        with ctx:
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                loss = self.model(tokens, mask)
+            loss.backward()
         return loss.detach()
+
+    def step(self, tokens: torch.Tensor, mask: MaskSpec) -> torch.Tensor:
+        loss = self.forward_backward(tokens, mask)
+        self.opt.step()
+        return loss
 
 
 def train_flops_per_step(cfg: LMConfig, T: int, unmasked_pairs: int) -> float:

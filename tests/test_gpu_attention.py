@@ -166,6 +166,9 @@ def test_full_size_config2_one_head_against_gpu_evaluated_oracle():
     g = torch.Generator(device=dev).manual_seed(2)
     q1, k1, v1, do1 = (torch.randn(1, 1, t, 128, device=dev, generator=g).bfloat16() for _ in range(4))
     q, k, v, do = (x.expand(1, 16, t, 128).contiguous() for x in (q1, k1, v1, do1))
+    q9, k9, v9, do9 = (torch.randn(1, 1, t, 128, device=dev, generator=g).bfloat16() for _ in range(4))  # head 9 has its own data
+    for full, own in ((q, q9), (k, k9), (v, v9), (do, do9)):
+        full[:, 9:10] = own
     q.requires_grad_(True); k.requires_grad_(True); v.requires_grad_(True)
     out, lse = masked_attn(q, k, v, doc, link, plan=bm.plan)
     out.backward(do)
@@ -177,7 +180,12 @@ def test_full_size_config2_one_head_against_gpu_evaluated_oracle():
     assert (lse[:, :1] - rl).abs().max().item() <= LSE_TOL
     for a, b in ((q.grad, rdq), (k.grad, rdk), (v.grad, rdv)):
         assert ((a[:, :1].float() - b).norm() / b.norm()).item() <= GRAD_TOL
-    for h in range(1, 16):  # identical inputs per head: identical results (dq up to fp32 atomic ordering)
+    ro9, rl9, rdq9, rdk9, rdv9 = oattn.forward_backward(q9, k9, v9, dense, do9)
+    assert (out[:, 9:10].float() - ro9).abs().max().item() <= O_TOL
+    assert (lse[:, 9:10] - rl9).abs().max().item() <= LSE_TOL
+    for a, b in ((q.grad, rdq9), (k.grad, rdk9), (v.grad, rdv9)):
+        assert ((a[:, 9:10].float() - b).norm() / b.norm()).item() <= GRAD_TOL
+    for h in [x for x in range(1, 16) if x != 9]:  # identical inputs per head: identical results (dq up to fp32 atomic ordering)
         assert torch.equal(out[:, h], out[:, 0]) and torch.equal(k.grad[:, h], k.grad[:, 0]) and torch.equal(v.grad[:, h], v.grad[:, 0])
         assert (q.grad[:, h].float() - q.grad[:, 0].float()).abs().max().item() <= 2e-2
 
@@ -222,6 +230,39 @@ def test_full_size_32k_one_head_against_streamed_gpu_oracle_and_properties():
     _, _, dv12 = _attn_bwd(q, k, v, out, (do.float() + do2.float()).bfloat16(), lse, doc, link, None, None, bm.plan, scale)
     lin = (dv12.float() - dv.float() - dv2.float()).norm() / dv12.float().norm()
     assert lin.item() <= 1e-2
+
+
+@pytest.mark.parametrize("mask,mi,b,h", [("doc_causal", 0, 0, 3), ("link_p05", 1, 1, 11)])
+def test_full_size_32k_other_bench_masks_one_slice_against_streamed_gpu_oracle(mask, mi, b, h):
+    """The other two masks of the benchmark sweep at its full size and with its seeds (1003 + 10 * mask + batch): one
+    (batch, head) slice each against the slab-streamed fp32 oracle."""
+    from tagseq2tagseq_b200 import build_block_map, read_status, synth
+    from tagseq2tagseq_b200.attention import _attn_bwd, _attn_fwd
+    torch.backends.cuda.matmul.allow_tf32 = False
+    dev = torch.device("cuda")
+    packs = [synth.config3_pack(1003 + 10 * mi + i, mask) for i in range(2)]
+    doc_np, link_np = synth.stack_packs(packs)
+    doc = torch.from_numpy(doc_np).to(dev)
+    link = None if link_np is None else torch.from_numpy(link_np).to(dev)
+    bm = build_block_map(doc, link)
+    g = torch.Generator(device=dev).manual_seed(40 + mi)
+    B, H, T, D = 2, 16, 32768, 128
+    q, k, v, do = (torch.randn(B, H, T, D, device=dev, generator=g).bfloat16() for _ in range(4))
+    scale = D ** -0.5
+    out, lse = _attn_fwd(q, k, v, doc, link, None, None, bm.plan, scale)
+    dq, dk, dv = _attn_bwd(q, k, v, out, do, lse, doc, link, None, None, bm.plan, scale)
+    torch.cuda.synchronize()
+    assert read_status(bm.plan) == 0
+    doc_b, link_b = doc_np[b], None if link_np is None else link_np[b]
+
+    def slab_mask(q0, q1):
+        return torch.from_numpy(om.class_mask_dense(doc_b, None, None, link_b, q_range=(q0, q1))).to(dev)
+
+    ro, rl, rdq, rdk, rdv = oattn.forward_backward_streamed(q[b, h], k[b, h], v[b, h], do[b, h], slab_mask, scale)
+    assert (out[b, h].float() - ro).abs().max().item() <= O_TOL
+    assert (lse[b, h] - rl).abs().max().item() <= LSE_TOL
+    for a, r in ((dq[b, h], rdq), (dk[b, h], rdk), (dv[b, h], rdv)):
+        assert ((a.float() - r).norm() / r.norm()).item() <= GRAD_TOL
 
 
 def test_argument_errors():

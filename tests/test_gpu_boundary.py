@@ -1,0 +1,143 @@
+"""Boundary behaviour on the GPU: a bounded wait that runs out, a plan that belongs to another call, the operator under
+torch.compile and torch.library.opcheck, the `causal` creator, and a batch served by a one-sequence mask."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oattn
+from oracle import masks as om
+
+pytestmark = pytest.mark.gpu
+
+O_TOL, LSE_TOL, GRAD_TOL = 2e-2, 1e-2, 1e-2
+
+
+def test_bounded_wait_runs_out_and_reports_its_code():
+    """The one way a device wait may fail here: nothing ever arrives on the barrier, the poll limit (4096 in the
+    self-test library) is reached, the code lands in the status word and the kernel returns.  ts2ts_read_status hands
+    the code back as its return value."""
+    from tagseq2tagseq_b200 import _lib, build
+    L = _lib.lib()
+    st = ctypes.CDLL(build.SELFTEST_LIB)
+    st.ts2ts_selftest_bounded_wait.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+    st.ts2ts_selftest_spin_limit.restype = ctypes.c_uint
+    assert st.ts2ts_selftest_spin_limit() <= 1 << 16
+    dev = torch.device("cuda")
+    plan = torch.zeros(L.ts2ts_plan_bytes(1, 128), dtype=torch.uint8, device=dev)  # status word 0 = 0
+    cycles = torch.zeros(1, dtype=torch.int64, device=dev)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    assert st.ts2ts_selftest_bounded_wait(plan.data_ptr(), 77, cycles.data_ptr(), stream) == 0
+    out = ctypes.c_int32(0)
+    rc = L.ts2ts_read_status(plan.data_ptr(), stream, ctypes.byref(out))
+    assert rc == 1077 and out.value == 1077            # > 0: the recorded code, as include/ts2ts_attn.h promises
+    assert b"1077" in L.ts2ts_last_error_string()
+    assert 0 < int(cycles.item()) < 50_000_000         # gave up after thousands of polls, not after seconds
+    torch.cuda.synchronize()                           # the context is still usable
+    assert float(torch.ones(4, device=dev).sum()) == 4.0
+
+
+def test_plan_of_another_call_is_refused_with_a_status_code():
+    """A plan built for (B=1, T=512) handed to calls with T=384: the buffer is large enough, so the host check passes,
+    but the stamp the pre-pass left does not match and both kernels return without touching a list."""
+    from tagseq2tagseq_b200 import build_block_map, read_status
+    from tagseq2tagseq_b200.attention import _attn_bwd, _attn_fwd
+    dev = torch.device("cuda")
+    plan = build_block_map(torch.zeros((1, 512), dtype=torch.int32, device=dev)).plan
+    doc = torch.zeros((1, 384), dtype=torch.int32, device=dev)
+    q, k, v = (torch.randn(1, 2, 384, 128, device=dev).bfloat16() for _ in range(3))
+    out, lse = _attn_fwd(q, k, v, doc, None, None, None, plan, 0.1)
+    assert read_status(plan) == 1900
+    good = build_block_map(doc).plan
+    out, lse = _attn_fwd(q, k, v, doc, None, None, None, good, 0.1)
+    assert read_status(good) == 0
+    plan2 = build_block_map(torch.zeros((1, 512), dtype=torch.int32, device=dev)).plan
+    _attn_bwd(q, k, v, out, torch.ones_like(q), lse, doc, None, None, None, plan2, 0.1)
+    assert read_status(plan2) == 2901
+    never_built = torch.zeros_like(good)
+    _attn_fwd(q, k, v, doc, None, None, None, never_built, 0.1)
+    assert read_status(never_built) == 1900
+
+
+def _masked_case(t, seed, dev):
+    from tagseq2tagseq_b200 import synth
+    pack = synth.make_pack(seed, t, 50, 4, 200, p_link=0.25)
+    doc = torch.from_numpy(pack.doc_ids)[None].to(dev)
+    link = torch.from_numpy(pack.link_bits)[None].to(dev)
+    dense = torch.from_numpy(om.class_mask_dense(pack.doc_ids, None, None, pack.link_bits))[None]
+    g = torch.Generator().manual_seed(seed)
+    q, k, v, do = (torch.randn(1, 2, t, 64, generator=g).bfloat16() for _ in range(4))
+    return doc, link, dense, q, k, v, do
+
+
+def test_operator_under_torch_compile_dynamic_and_opcheck():
+    """The reference compiles its backbone with dynamic=True (main.py:387-397), so the operator must trace with fake
+    tensors, stay one graph node and accept a sequence length it was not first compiled for."""
+    from tagseq2tagseq_b200 import build_block_map
+    from tagseq2tagseq_b200.attention import masked_attn
+    dev = torch.device("cuda")
+
+    def fn(q, k, v, doc, link, plan):
+        out, lse = masked_attn(q * 1.0, k, v, doc, link, plan=plan)
+        return out * 2.0, lse
+
+    compiled = torch.compile(fn, dynamic=True, fullgraph=True, backend="aot_eager")
+    for t, seed in ((256, 1), (384, 2)):
+        doc, link, dense, q, k, v, do = _masked_case(t, seed, dev)
+        plan = build_block_map(doc, link).plan
+        qd, kd, vd = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+        out, lse = compiled(qd, kd, vd, doc, link, plan)
+        out.backward(do.to(dev))
+        ro, rl, rdq, rdk, rdv = oattn.forward_backward(q, k, v, dense, do * 2.0)
+        assert (out.float().cpu() - 2.0 * ro).abs().max().item() <= 2 * O_TOL
+        assert (lse.cpu() - rl).abs().max().item() <= LSE_TOL
+        for a, b in ((qd.grad, rdq), (kd.grad, rdk), (vd.grad, rdv)):
+            assert ((a.float().cpu() - b).norm() / b.norm()).item() <= GRAD_TOL
+    doc, link, dense, q, k, v, do = _masked_case(256, 3, dev)
+    plan = build_block_map(doc, link).plan
+    args = (q.to(dev), k.to(dev), v.to(dev), doc, link, None, None, plan, 0.125)
+    torch.library.opcheck(torch.ops.ts2ts.masked_attn_fwd.default, args,
+                          test_utils=("test_schema", "test_faketensor", "test_autograd_registration"))
+
+
+def test_causal_creator_matches_plain_causal_attention():
+    """`causal` of the reference's registry (block_mask_creator.py:143-172): block map and attention against the oracle."""
+    from oracle import block_map as obm
+    from tagseq2tagseq_b200 import mask_spec as ms
+    from tagseq2tagseq_b200.attention import flex_attention
+    dev = torch.device("cuda")
+    t = 700
+    spec = ms.make_mask_creator_callable("causal")(tokens=torch.zeros((1, t), dtype=torch.int64, device=dev), doc_spans=[])
+    dense = np.tril(np.ones((t, t), dtype=bool))
+    assert np.array_equal(spec.block_map(with_lists=True).state[0].cpu().numpy(), obm.block_states(dense))
+    g = torch.Generator().manual_seed(4)
+    q, k, v, do = (torch.randn(1, 2, t, 128, generator=g).bfloat16() for _ in range(4))
+    qd, kd, vd = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+    out, lse = flex_attention(qd, kd, vd, block_mask=spec, return_lse=True)
+    out.backward(do.to(dev))
+    ro, rl, rdq, rdk, rdv = oattn.forward_backward(q, k, v, torch.from_numpy(dense)[None], do)
+    assert (out.float().cpu() - ro).abs().max().item() <= O_TOL and (lse.cpu() - rl).abs().max().item() <= LSE_TOL
+    for a, b in ((qd.grad, rdq), (kd.grad, rdk), (vd.grad, rdv)):
+        assert ((a.float().cpu() - b).norm() / b.norm()).item() <= GRAD_TOL
+
+
+def test_one_sequence_mask_serves_a_batch_and_expanded_inputs():
+    """The reference's BlockMask has B=None and broadcasts; here a one-sequence MaskSpec is expanded once per batch size
+    (its plan is cached) and stride-0 q/k/v views are copied instead of being rejected."""
+    from tagseq2tagseq_b200.attention import flex_attention
+    from tagseq2tagseq_b200.mask_spec import MaskSpec
+    dev = torch.device("cuda")
+    doc, link, dense, q, k, v, do = _masked_case(300, 7, dev)
+    spec = MaskSpec(doc_ids=doc, link_bits=link)
+    qb = q.to(dev).expand(3, -1, -1, -1)  # stride 0 over the batch
+    kb, vb = k.to(dev).expand(3, -1, -1, -1), v.to(dev).expand(3, -1, -1, -1)
+    out = flex_attention(qb, kb, vb, block_mask=spec)
+    plan_first = spec.expanded(3).plan
+    out2 = flex_attention(qb, kb, vb, block_mask=spec)
+    assert spec.expanded(3).plan.data_ptr() == plan_first.data_ptr()  # no second pre-pass
+    ro = oattn.forward_backward(q, k, v, dense, do)[0]
+    for b in range(3):
+        assert (out[b].float().cpu() - ro[0]).abs().max().item() <= O_TOL
+    assert torch.equal(out, out2)

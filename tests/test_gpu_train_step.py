@@ -1,0 +1,129 @@
+"""The training-step harness around the operator: the attention call inside a decoder block against the oracle
+(strided views of the fused QKV projection, bf16 autocast), and a two-rank DDP step whose gradients must equal the
+mean of the two ranks' single-GPU gradients (two processes share the one GPU and talk over gloo; NCCL needs one GPU
+per rank)."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention as oattn
+from oracle import masks as om
+
+pytestmark = pytest.mark.gpu
+
+
+def _small_cfg():
+    from tagseq2tagseq_b200.train_step import LMConfig
+    return LMConfig(n_layers=2, d_model=128, n_heads=2, head_dim=64, mlp_hidden=256, vocab=512)
+
+
+def test_attention_inside_a_block_matches_the_oracle():
+    from tagseq2tagseq_b200 import synth
+    from tagseq2tagseq_b200.attention import masked_attn
+    from tagseq2tagseq_b200.mask_spec import MaskSpec
+    from tagseq2tagseq_b200.train_step import Block, apply_rope, rope_tables
+    dev = torch.device("cuda")
+    torch.manual_seed(0)
+    cfg = _small_cfg()
+    t = 600
+    pack = synth.make_pack(21, t, 60, 8, 300, p_link=0.3)
+    spec = MaskSpec(doc_ids=torch.from_numpy(pack.doc_ids)[None].to(dev), link_bits=torch.from_numpy(pack.link_bits)[None].to(dev))
+    dense = torch.from_numpy(om.class_mask_dense(pack.doc_ids, None, None, pack.link_bits))[None]
+    blk = Block(cfg).to(dev)
+    x = torch.randn(1, t, cfg.d_model, device=dev)
+    cos, sin = (c.to(torch.bfloat16)[None, :, None, None, :] for c in rope_tables(t, cfg.head_dim, cfg.rope_base, dev))
+    with torch.autocast("cuda", dtype=torch.bfloat16):
+        # the block's own first half, step by step, keeping q, k, v as leaves of a small graph
+        qkv = blk.qkv(blk.ln1(x)).view(1, t, 3, cfg.n_heads, cfg.head_dim)
+        assert qkv.dtype == torch.bfloat16
+        qk = apply_rope(qkv[:, :, :2], cos, sin).detach().requires_grad_(True)
+        vv = qkv[:, :, 2].detach().requires_grad_(True)
+        q, k, v = qk[:, :, 0].permute(0, 2, 1, 3), qk[:, :, 1].permute(0, 2, 1, 3), vv.permute(0, 2, 1, 3)
+        assert not q.is_contiguous() and q.stride(-1) == 1          # consumed in place through the TMA strides
+        out, lse = masked_attn(q, k, v, spec.doc_ids, spec.link_bits, plan=spec.plan)
+        do = torch.randn_like(out)
+        out.backward(do)
+        whole = blk(x, spec, cos, sin)                               # and the block as a whole runs
+    assert torch.isfinite(whole.float()).all()
+    ro, rl, rdq, rdk, rdv = oattn.forward_backward(q.detach().cpu(), k.detach().cpu(), v.detach().cpu(), dense, do.cpu())
+    assert (out.float().cpu() - ro).abs().max().item() <= 2e-2
+    assert (lse.cpu() - rl).abs().max().item() <= 1e-2
+    gq, gk = qk.grad[:, :, 0].permute(0, 2, 1, 3), qk.grad[:, :, 1].permute(0, 2, 1, 3)
+    gv = vv.grad.permute(0, 2, 1, 3)
+    for a, b in ((gq, rdq), (gk, rdk), (gv, rdv)):
+        assert ((a.float().cpu() - b).norm() / b.norm()).item() <= 1e-2
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _batch(rank, cfg, t, dev):
+    from tagseq2tagseq_b200 import synth
+    from tagseq2tagseq_b200.mask_spec import MaskSpec
+    pack = synth.make_pack(300 + rank, t, 60, 8, 300, p_link=0.2)
+    spec = MaskSpec(doc_ids=torch.from_numpy(pack.doc_ids)[None].to(dev), link_bits=torch.from_numpy(pack.link_bits)[None].to(dev))
+    g = torch.Generator().manual_seed(900 + rank)
+    return torch.randint(0, cfg.vocab, (1, t + 1), generator=g).to(dev), spec
+
+
+def _ddp_worker(rank, world, port, bf16_grads, out):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from tagseq2tagseq_b200.train_step import TrainStep
+        dev = torch.device("cuda", 0)
+        torch.cuda.set_device(dev)
+        cfg, t = _small_cfg(), 512
+        # what each rank would compute alone, from the same initial weights
+        alone = []
+        for r in range(world):
+            ts1 = TrainStep(cfg, dev, world=1, seed=5)
+            tok, spec = _batch(r, cfg, t, dev)
+            ts1.forward_backward(tok, spec)
+            alone.append([p.grad.detach().float().clone() for p in ts1.model.parameters()])
+        ts = TrainStep(cfg, dev, world=world, seed=5, bf16_grads=bf16_grads)
+        tok, spec = _batch(rank, cfg, t, dev)
+        loss = ts.forward_backward(tok, spec)
+        torch.cuda.synchronize()
+        worst = 0.0
+        for p, g0, g1 in zip(ts.model.parameters(), alone[0], alone[1]):
+            want = (g0 + g1) / 2
+            worst = max(worst, ((p.grad.float() - want).norm() / want.norm().clamp_min(1e-12)).item())
+        # without the all-reduce (no_sync) the gradients are this rank's own
+        ts.forward_backward(tok, spec, sync=False)
+        own = max(((p.grad.float() - g).norm() / g.norm().clamp_min(1e-12)).item() for p, g in zip(ts.model.parameters(), alone[rank]))
+        loss2 = ts.step(tok, spec)                                   # and a full optimizer step runs
+        out.put((rank, worst, own, float(loss), float(loss2), ts.grad_bytes_per_step))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("bf16_grads", [False, True])
+def test_two_rank_ddp_gradients_are_the_mean_of_single_rank_gradients(bf16_grads):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    out = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_ddp_worker, args=(r, 2, port, bf16_grads, out)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = [out.get(timeout=300) for _ in range(2)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    n_params = None
+    for rank, worst, own, loss, loss2, gbytes in got:
+        # fp32 buckets: only the dq reduction order differs between runs; bf16 buckets: one bf16 rounding per rank
+        assert worst <= (2e-2 if bf16_grads else 5e-3), (rank, worst)
+        assert own <= 5e-3, (rank, own)
+        assert np.isfinite(loss) and np.isfinite(loss2)
+        n_params = gbytes // (2 if bf16_grads else 4)
+    assert n_params > 0

@@ -3,6 +3,7 @@ import math
 
 import numpy as np
 import pytest
+import torch
 
 from oracle import masks as om
 from tagseq2tagseq_b200 import mask_spec as ms
@@ -57,9 +58,13 @@ def test_match_links_enforces_dag():
 
 
 def test_registry_behaviour():
-    assert ms.list_mask_creators() == ["doc_causal"]
+    # the same four names, in the same order, as the reference's registry (block_mask_creator.py:251-256)
+    assert ms.list_mask_creators() == ["doc_causal", "causal", "full", "doc_bidirectional"]
     with pytest.raises(ValueError, match="Unknown mask creator"):
         ms.get_mask_creator("sliding")
+    for name in ("full", "doc_bidirectional"):  # known names whose masks the causal kernels cannot compute
+        with pytest.raises(NotImplementedError, match="non-causal"):
+            ms.get_mask_creator(name)(torch.zeros((1, 8), dtype=torch.int64), [])
     fn = ms.make_mask_creator_callable("doc_causal")
     with pytest.raises(ValueError, match="tokens"):
         fn(doc_spans=[])

@@ -51,9 +51,13 @@ def test_noalloc_backward_matches_workspace_backward_twice(t, h, d, p):
         code = L.ts2ts_attn_bwd(*_bwd_args(q, k, v, out, do, lse, doc, link, plan, *ref, scale), ws.data_ptr(), ws.numel(), stream)
         assert code == 0, L.ts2ts_last_error_string()
         got = [torch.full_like(q, float("nan")) for _ in range(3)]
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(dev)[0]
         code = L.ts2ts_attn_bwd_noalloc(*_bwd_args(q, k, v, out, do, lse, doc, link, plan, *got, scale), stream)
         assert code == 0, L.ts2ts_last_error_string()
         torch.cuda.synchronize()
+        if call > 0:  # set-up happened in the first call; from then on the entry point must not take device memory
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
         assert read_status(plan) == 0
         assert torch.equal(got[1], ref[1]) and torch.equal(got[2], ref[2])
         rel = ((got[0].float() - ref[0].float()).norm() / ref[0].float().norm()).item()
