@@ -275,10 +275,11 @@ def run_ours(args, rank, world, device):
     h2d = 4 * tens * len(masks) + mask_bytes
     d2h = (4 * tens + B * H * T * 4) * len(masks)
 
-    ref_mask = ref_format = None
+    ref_mask = ref_format = mask_create = None
     if world == 1 and WORKLOAD == "attn_fwd_bwd_32k_mask_sweep":
         ref_mask = reference_block_mask_time(masks[0]["packs"][0], device)
         ref_format = reference_format_mask_time(masks[2]["packs"][0], q, k, v, do, device)
+        mask_create = mask_create_time(device)
 
     train = None
     if WORKLOAD == "attn_fwd_bwd_32k_mask_sweep" and not args.no_train:
@@ -345,6 +346,8 @@ def run_ours(args, rank, world, device):
         line["block_map_vs_reference"] = ref_mask
     if ref_format is not None:
         line["reference_format_mask"] = ref_format
+    if mask_create is not None:
+        line["mask_create"] = mask_create
     emit(line)
 
 
@@ -602,34 +605,105 @@ def cpu_sample():
     return torch.from_numpy(dense), q, k, v, do, pairs, heads, t
 
 
-def reference_mask_and_step():
-    """The reference's own CPU code for this path, when its sources are present under baseline/_ref: dense mask from
-    CrossDocLinkMaskCreator.build_dense_mask_for_visualization (model/graph_traversal/cross_doc_mask.py:371-409),
-    attention = fp32 F.scaled_dot_product_attention + autograd (FlexAttention has no CPU backward).
-    Returns None when baseline/_ref is absent, so that the oracle port is used instead."""
+def load_reference_mask_modules():
+    """The reference's link_detector.py and cross_doc_mask.py loaded by path from baseline/_ref (bare `model` packages:
+    model/__init__ needs tunalab, which is absent).  None when baseline/_ref is absent or does not import."""
     import importlib.util
     import types
-    from types import SimpleNamespace
     ref = os.path.join(ROOT, "baseline", "_ref")
     path = os.path.join(ref, "model", "graph_traversal", "cross_doc_mask.py")
     if not os.path.exists(path):
         return None
     try:
-        for name in ("model", "model.graph_traversal"):  # bare packages: model/__init__ needs tunalab, which is absent
+        for name in ("model", "model.graph_traversal"):
             if name not in sys.modules:
                 m = types.ModuleType(name)
                 m.__path__ = []
                 sys.modules[name] = m
         mods = {}
         for name, rel in (("model.graph_traversal.link_detector", "link_detector.py"), ("model.graph_traversal.cross_doc_mask", "cross_doc_mask.py")):
+            if name in sys.modules and hasattr(sys.modules[name], "__file__"):
+                mods[name] = sys.modules[name]
+                continue
             spec = importlib.util.spec_from_file_location(name, os.path.join(ref, "model", "graph_traversal", rel))
             mod = importlib.util.module_from_spec(spec)
             sys.modules[name] = mod
             spec.loader.exec_module(mod)
             mods[name] = mod
-        cdm = mods["model.graph_traversal.cross_doc_mask"]
-    except Exception:
+        return mods["model.graph_traversal.link_detector"], mods["model.graph_traversal.cross_doc_mask"]
+    except Exception:  # noqa: BLE001
         return None
+
+
+def mask_create_time(device):
+    """One micro-batch's mask creation, CrossDocLinkMaskCreator.__call__ to a usable mask object, timed on the same
+    document spans and detected links (T = 16384, the config-2 pack, every link placed in the middle of its source
+    document, max_grants = 256): this package's creator (host matching and segment classes, per-token ids and block-map
+    pre-pass on the device) and, when baseline/_ref is present, the reference's own creator
+    (model/graph_traversal/cross_doc_mask.py:302-369: per-grant slice writes + torch create_block_mask on the GPU).
+    Wall clock around a device synchronisation, 2 warm-ups, median of 5."""
+    from types import SimpleNamespace
+    from tagseq2tagseq_b200 import mask_spec as ms
+    from tagseq2tagseq_b200 import synth
+    pack = synth.config2_pack()
+    lengths = pack.lengths
+    starts = np.concatenate([[0], np.cumsum(lengths)[:-1]])
+    t = int(pack.doc_ids.shape[0])
+    spans = [SimpleNamespace(doc_id=i, start=int(starts[i]), end=int(starts[i] + lengths[i]), raw_identifier=f"doc{i}") for i in range(len(lengths))]
+    found = [(int(starts[a] + max(1, lengths[a] // 2)), f"doc{b_}") for a, b_ in pack.links]
+    tokens = torch.zeros((1, t), dtype=torch.int64, device=device)
+
+    def detector(link_cls):
+        class Det:
+            def detect_links(self, ids):
+                return [link_cls(p_, s_) for p_, s_ in found]
+
+            def index_doc_span(self, span):
+                return span.raw_identifier
+        return Det()
+
+    def timed(fn):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize(device)
+        out = []
+        for _ in range(5):
+            t0 = time.perf_counter()
+            fn()
+            torch.cuda.synchronize(device)
+            out.append((time.perf_counter() - t0) * 1e3)
+        return statistics.median(out)
+
+    ours = ms.CrossDocLinkMaskCreator(detector(ms.LinkInfo), max_grants=256)
+    res = {"T": t, "docs": len(spans), "links": len(found), "max_grants": 256,
+           "ours_ms": timed(lambda: ours(tokens, spans).plan)}
+    mods = load_reference_mask_modules()
+    if mods is None:
+        res["reference_ms"] = None
+        res["reference"] = "baseline/_ref absent"
+        return res
+    ld, cdm = mods
+    try:
+        theirs = cdm.CrossDocLinkMaskCreator(link_detector=detector(ld.LinkInfo), max_grants=256)
+        res["reference_ms"] = timed(lambda: theirs(tokens, spans))
+        res["reference"] = "CrossDocLinkMaskCreator.__call__ of baseline/_ref on the same GPU"
+    except Exception as exc:  # noqa: BLE001 - the reference's eager mask build may not fit or trace on this box
+        res["reference_ms"] = None
+        res["reference"] = "failed: " + str(exc).splitlines()[0][:160]
+    torch.cuda.empty_cache()
+    return res
+
+
+def reference_mask_and_step():
+    """The reference's own CPU code for this path, when its sources are present under baseline/_ref: dense mask from
+    CrossDocLinkMaskCreator.build_dense_mask_for_visualization (model/graph_traversal/cross_doc_mask.py:371-409),
+    attention = fp32 F.scaled_dot_product_attention + autograd (FlexAttention has no CPU backward).
+    Returns None when baseline/_ref is absent, so that the oracle port is used instead."""
+    from types import SimpleNamespace
+    mods = load_reference_mask_modules()
+    if mods is None:
+        return None
+    cdm = mods[1]
 
     class NoLinks:
         def detect_links(self, ids):

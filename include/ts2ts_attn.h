@@ -67,6 +67,13 @@ int ts2ts_block_map(const int32_t* doc_ids, const int32_t* q_row_ids, const int3
                     uint8_t* state, int32_t* kv_cnt, int32_t* kv_idx, int32_t* full_cnt, int32_t* full_idx,
                     int32_t* q_cnt, int32_t* q_idx, int32_t* full_q_cnt, int32_t* full_q_idx, void* stream);
 
+/* Per-token class ids from a table of segments, filled on the device: out[t] = ids[j] for bounds[j] <= t < bounds[j+1]
+ * (bounds: device int32[n_seg + 1], ascending; ids: device int32[n_seg]), -1 for tokens before bounds[0] or from
+ * bounds[n_seg] on.  With the segments cut at the start and end of every grant this writes q_row_ids / kv_col_ids of
+ * the cross_doc_link mask; it replaces the per-grant slice assignments into [T]-long int64 bit tensors of
+ * _build_grant_bitmasks (model/graph_traversal/cross_doc_mask.py:258-294).  out: device int32[T]. */
+int ts2ts_segment_ids(const int32_t* bounds, const int32_t* ids, int n_seg, int T, int32_t* out, void* stream);
+
 /* Forward: out = softmax(scale * q k^T + mask) v, lse = natural-log row sums, fp32 [B,H,T].
  * A row with no allowed key gets out = 0 and lse = -inf.  Replaces the forward of
  * flex_attention(q, k, v, block_mask=...) (torch/nn/attention/flex_attention.py:1468). */

@@ -19,6 +19,7 @@ SYMBOLS = {
     "ts2ts_last_error_string": (c_char_p, []),
     "ts2ts_plan_bytes": (c_size_t, [c_int, c_int]),
     "ts2ts_block_map": (c_int, [c_void_p] * 4 + [c_int] * 4 + [c_void_p, c_size_t] + [c_void_p] * 9 + [c_void_p]),
+    "ts2ts_segment_ids": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "ts2ts_attn_fwd": (c_int, [c_void_p] * 3 + [POINTER(c_int64)] * 3 + [c_int] * 4 + [c_float] + [c_void_p] * 4 + [c_int] * 2
                        + [c_void_p, c_size_t, c_void_p, POINTER(c_int64), c_void_p, c_void_p]),
     "ts2ts_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 4),

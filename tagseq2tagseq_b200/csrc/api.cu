@@ -17,6 +17,7 @@ cudaError_t launch_block_map(PlanView P, MaskArgs M, uint8_t* state_out, int32_t
 int launch_fwd(const void* q, const void* k, const void* v, void* out, float* lse, const int64_t* sq, const int64_t* sk,
                const int64_t* sv, const int64_t* so, int B, int H, int T, int D, float scale, PlanView P, MaskArgs M,
                cudaStream_t stream);
+cudaError_t launch_segment_ids(const int32_t* bounds, const int32_t* ids, int n_seg, int T, int32_t* out, cudaStream_t stream);
 size_t bwd_workspace_bytes(int B, int H, int T, int D);
 int launch_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout, const float* lse, const int64_t* sq,
                const int64_t* sk, const int64_t* sv, const int64_t* so, const int64_t* sdo, int B, int H, int T, int D, float scale,
@@ -118,6 +119,15 @@ int ts2ts_block_map(const int32_t* doc_ids, const int32_t* q_row_ids, const int3
   cudaError_t e = launch_block_map(P, mask_args(doc_ids, q_row_ids, kv_col_ids, link_bits, R, W), state, kv_cnt, kv_idx, full_cnt,
                                    full_idx, q_cnt, q_idx, full_q_cnt, full_q_idx, static_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(-50, "block map launch failed: %s", cudaGetErrorString(e));
+  return 0;
+}
+
+int ts2ts_segment_ids(const int32_t* bounds, const int32_t* ids, int n_seg, int T, int32_t* out, void* stream) {
+  if (T <= 0 || T > kMaxT) return fail(-1, "T must be in 1..%d (got %d)", kMaxT, T);
+  if (n_seg < 0 || n_seg > kMaxT) return fail(-1, "n_seg must be in 0..%d (got %d)", kMaxT, n_seg);
+  if (out == nullptr || bounds == nullptr || (n_seg > 0 && ids == nullptr)) return fail(-3, "bounds / ids / out: null pointer");
+  cudaError_t e = launch_segment_ids(bounds, ids, n_seg, T, out, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(-50, "segment id launch failed: %s", cudaGetErrorString(e));
   return 0;
 }
 

@@ -164,6 +164,26 @@ __global__ void stamp_kernel(PlanView P, int link_t_rows) {
   P.status[kLinkTRows] = link_t_rows;
 }
 
+// Per-token ids from a sorted table of segments: token t gets ids[j] for bounds[j] <= t < bounds[j + 1], and -1 before
+// bounds[0] or from bounds[n_seg] on.  This is the device-side half of what the reference does with one slice
+// assignment per grant (cross_doc_mask.py:277-294): the host only works out the few hundred segment boundaries.
+__global__ void __launch_bounds__(256) segment_ids_kernel(const int32_t* __restrict__ bounds, const int32_t* __restrict__ ids,
+                                                          int n_seg, int T, int32_t* __restrict__ out) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= T) return;
+  int lo = 0, hi = n_seg + 1;  // first boundary > t, by bisection over bounds[0 .. n_seg]
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (__ldg(bounds + mid) <= t) lo = mid + 1; else hi = mid;
+  }
+  out[t] = (lo == 0 || lo > n_seg) ? -1 : __ldg(ids + lo - 1);
+}
+
+cudaError_t launch_segment_ids(const int32_t* bounds, const int32_t* ids, int n_seg, int T, int32_t* out, cudaStream_t stream) {
+  segment_ids_kernel<<<(T + 255) / 256, 256, 0, stream>>>(bounds, ids, n_seg, T, out);
+  return cudaGetLastError();
+}
+
 // Host entry: fills the plan; optional BlockMask-shaped outputs may be null.
 cudaError_t launch_block_map(PlanView P, MaskArgs M, uint8_t* state_out, int32_t* kv_cnt, int32_t* kv_idx,
                              int32_t* full_cnt, int32_t* full_idx, int32_t* q_cnt, int32_t* q_idx, int32_t* full_q_cnt,

@@ -238,6 +238,57 @@ def grant_classes(seq_len: int, grants: Sequence[Tuple[int, int, int, int]]):
     return row_ids, col_ids, link.view(np.int64)
 
 
+def grant_segments(grants: Sequence[Tuple[int, int, int, int]]):
+    """The same classes as ``grant_classes`` worked out on segment boundaries instead of tokens.
+
+    The set of grants that covers a token only changes where a grant starts or ends, so there are at most 2 G + 1
+    segments per side however long the sequence is.  Returns, for the query side and the key side, (bounds int32[S+1],
+    ids int32[S]) with id -1 for segments no grant covers, and link_bits int64[R, W]: bit c of row r is set when some
+    grant covers both row class r and column class c.  Classes are numbered in order of first appearance."""
+    def side(ranges):
+        pts = sorted({p for a, b in ranges for p in (a, b)})
+        if not pts:
+            return np.zeros(1, dtype=np.int32), np.zeros(0, dtype=np.int32), []
+        bounds = np.asarray(pts, dtype=np.int32)
+        starts = np.asarray([a for a, _ in ranges], dtype=np.int64)
+        ends = np.asarray([b for _, b in ranges], dtype=np.int64)
+        cover = (starts[None, :] <= bounds[:-1, None]) & (bounds[:-1, None] < ends[None, :])  # [S, G]
+        ids, patterns, seen = np.full(len(pts) - 1, -1, dtype=np.int32), [], {}
+        for j in range(len(pts) - 1):
+            if not cover[j].any():
+                continue
+            key = cover[j].tobytes()
+            if key not in seen:
+                seen[key] = len(patterns)
+                patterns.append(cover[j])
+            ids[j] = seen[key]
+        return bounds, ids, patterns
+
+    qb, qi, rows = side([(g[0], g[1]) for g in grants])
+    kb, ki, cols = side([(g[2], g[3]) for g in grants])
+    R, C = max(1, len(rows)), len(cols)
+    W = max(1, (C + 63) // 64)
+    link = np.zeros((R, W), dtype=np.uint64)
+    if rows and cols:
+        hit = (np.stack(rows)[:, None, :] & np.stack(cols)[None, :, :]).any(axis=2)  # [R, C]
+        for c in range(C):
+            link[: len(rows), c >> 6] |= hit[:, c].astype(np.uint64) << np.uint64(c & 63)
+    return (qb, qi), (kb, ki), link.view(np.int64)
+
+
+def segment_ids(bounds: np.ndarray, ids: np.ndarray, seq_len: int, device: torch.device) -> torch.Tensor:
+    """int32[1, T] on the device from a segment table (``ts2ts_segment_ids``): one small host-to-device copy of the
+    table, then one kernel; nothing of length T crosses PCIe."""
+    table = torch.from_numpy(np.concatenate([bounds.astype(np.int32), ids.astype(np.int32)])).to(device, non_blocking=True)
+    out = torch.empty((1, seq_len), dtype=torch.int32, device=device)
+    n_seg = int(ids.shape[0])
+    with torch.cuda.device(device):
+        code = _lib.lib().ts2ts_segment_ids(table.data_ptr(), table.data_ptr() + 4 * (n_seg + 1), n_seg, seq_len, out.data_ptr(),
+                                            torch.cuda.current_stream(device).cuda_stream)
+    _lib.check(code, "ts2ts_segment_ids")
+    return out
+
+
 def from_reference(doc_spans: Sequence[Any], link_to_target: Optional[Dict[int, List[int]]], seq_len: int,
                    max_grants_cap: int = 64, device: Optional[torch.device] = None) -> MaskSpec:
     """MaskSpec equal to the reference's mask for these spans and matched links
@@ -249,6 +300,10 @@ def from_reference(doc_spans: Sequence[Any], link_to_target: Optional[Dict[int, 
     grants = ordered_grants(seq_len, doc_spans, link_to_target, max_grants_cap)
     if not grants:
         return MaskSpec(doc_ids=ids)
+    if torch.device(device).type == "cuda":  # classes on segment boundaries (host, O(G^2)); per-token ids filled on the device
+        (qb, qi), (kb, ki), link = grant_segments(grants)
+        return MaskSpec(doc_ids=ids, link_bits=torch.from_numpy(link)[None].to(device),
+                        q_row_ids=segment_ids(qb, qi, seq_len, device), kv_col_ids=segment_ids(kb, ki, seq_len, device))
     row, col, link = grant_classes(seq_len, grants)
     return MaskSpec(doc_ids=ids, link_bits=torch.from_numpy(link)[None].to(device),
                     q_row_ids=torch.from_numpy(row)[None].to(device), kv_col_ids=torch.from_numpy(col)[None].to(device))

@@ -141,3 +141,36 @@ def test_one_sequence_mask_serves_a_batch_and_expanded_inputs():
     for b in range(3):
         assert (out[b].float().cpu() - ro[0]).abs().max().item() <= O_TOL
     assert torch.equal(out, out2)
+
+
+def test_segment_ids_filled_on_the_device_and_reference_format_adapter():
+    """ts2ts_segment_ids against a numpy expansion (empty table, gaps, a table that ends before T), and from_reference
+    on the GPU -- classes from segments, ids filled by the kernel -- against the host construction on reference-style
+    grants that start in the middle of their source documents."""
+    from types import SimpleNamespace
+    from tagseq2tagseq_b200 import mask_spec as ms
+    dev = torch.device("cuda")
+    t = 1000
+    for bounds, ids in (([0], []), ([5, 17, 400, 401, 999], [3, -1, 0, 7]), ([0, 1000], [2]), ([10, 20, 30], [1, 1])):
+        got = ms.segment_ids(np.asarray(bounds, dtype=np.int32), np.asarray(ids, dtype=np.int32), t, dev)[0].cpu().numpy()
+        want = np.full(t, -1, dtype=np.int32)
+        for j, v in enumerate(ids):
+            want[bounds[j]:bounds[j + 1]] = v
+        assert np.array_equal(got, want)
+    rng = np.random.default_rng(3)
+    lengths = rng.integers(20, 120, size=14)
+    starts = np.concatenate([[0], np.cumsum(lengths)[:-1]])
+    t = int(lengths.sum())
+    spans = [SimpleNamespace(doc_id=i, start=int(starts[i]), end=int(starts[i] + lengths[i])) for i in range(len(lengths))]
+    links = {}
+    for a in range(1, len(lengths)):
+        for b in range(a):
+            if rng.random() < 0.3:
+                links.setdefault(int(starts[a] + rng.integers(1, lengths[a])), []).append(b)
+    spec = ms.from_reference(spans, links, t, max_grants_cap=64, device=dev)
+    grants = ms.ordered_grants(t, spans, links, 64)
+    row, col, link = ms.grant_classes(t, grants)
+    want = om.class_mask_dense(ms.build_document_ids(t, spans), row, col, link)
+    got = om.class_mask_dense(spec.doc_ids[0].cpu().numpy(), spec.q_row_ids[0].cpu().numpy(), spec.kv_col_ids[0].cpu().numpy(),
+                              spec.link_bits[0].cpu().numpy())
+    assert np.array_equal(got, want)

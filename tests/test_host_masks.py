@@ -115,3 +115,44 @@ def test_fuzz_reference_format_adapter_against_oracle(seed):
     else:
         mine = om.doc_causal_dense(ids)
     assert np.array_equal(mine, ref)
+
+
+def _dense_from_classes(row, col, link, t):
+    lu = np.ascontiguousarray(link).view(np.uint64)
+    m = np.zeros((t, t), dtype=bool)
+    for q in range(t):
+        if row[q] < 0:
+            continue
+        words = lu[int(row[q])]
+        for k in range(t):
+            c = int(col[k])
+            m[q, k] = c >= 0 and bool((int(words[c >> 6]) >> (c & 63)) & 1)
+    return m
+
+
+def _expand_segments(bounds, ids, t):
+    out = np.full(t, -1, dtype=np.int32)
+    for j in range(len(ids)):
+        out[bounds[j]:bounds[j + 1]] = ids[j]
+    return out
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_grant_segments_describe_the_same_mask_as_grant_classes(seed):
+    """Classes worked out on the <= 2G+1 segment boundaries (what the device fill consumes) against the per-token
+    construction, on random, overlapping and duplicate grants."""
+    rng = np.random.default_rng(seed)
+    t = int(rng.integers(20, 120))
+    grants = []
+    for _ in range(int(rng.integers(0, 80))):
+        q0 = int(rng.integers(0, t - 1)); q1 = int(rng.integers(q0 + 1, t + 1))
+        k0 = int(rng.integers(0, t - 1)); k1 = int(rng.integers(k0 + 1, t + 1))
+        grants.append((q0, q1, k0, k1))
+    if grants and seed % 3 == 0:
+        grants.append(grants[0])
+    row, col, link = ms.grant_classes(t, grants)
+    (qb, qi), (kb, ki), link2 = ms.grant_segments(grants)
+    assert len(qi) <= 2 * len(grants) + 1 and len(ki) <= 2 * len(grants) + 1
+    a = _dense_from_classes(row, col, link, t)
+    b = _dense_from_classes(_expand_segments(qb, qi, t), _expand_segments(kb, ki, t), link2, t)
+    assert np.array_equal(a, b)
