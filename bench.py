@@ -275,11 +275,12 @@ def run_ours(args, rank, world, device):
     h2d = 4 * tens * len(masks) + mask_bytes
     d2h = (4 * tens + B * H * T * 4) * len(masks)
 
-    ref_mask = ref_format = mask_create = None
+    ref_mask = ref_format = mask_create = decode = None
     if world == 1 and WORKLOAD == "attn_fwd_bwd_32k_mask_sweep":
         ref_mask = reference_block_mask_time(masks[0]["packs"][0], device)
         ref_format = reference_format_mask_time(masks[2]["packs"][0], q, k, v, do, device)
         mask_create = mask_create_time(device)
+        decode = decode_step_bench(masks, q, k, v, device, per_mask[2]["fwd_ms"])
 
     train = None
     if WORKLOAD == "attn_fwd_bwd_32k_mask_sweep" and not args.no_train:
@@ -348,7 +349,39 @@ def run_ours(args, rank, world, device):
         line["reference_format_mask"] = ref_format
     if mask_create is not None:
         line["mask_create"] = mask_create
+    if decode is not None:
+        line["decode_step"] = decode
     emit(line)
+
+
+def decode_step_bench(masks, q, k, v, device, fwd_ms_full):
+    """One decoding step with KV reuse (ts2ts_attn_decode) at the workload's size: the newest token of each of the B
+    sequences against the cached K / V of all T tokens under the link_p30 mask, beside the time of the full forward
+    that the reference would recompute for that token.  HBM-bound: every allowed key's K and V row is read once."""
+    from tagseq2tagseq_b200.attention import masked_attn_decode
+    _, hbm_gbs, peak_kind = measured_peaks()
+    m = masks[2]
+    q1 = q[:, :, -1:].contiguous()
+    for _ in range(3):
+        out, lse = masked_attn_decode(q1, k, v, m["doc"], m["link"])
+    torch.cuda.synchronize(device)
+    reps = 50
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        out, lse = masked_attn_decode(q1, k, v, m["doc"], m["link"])
+    e1.record()
+    torch.cuda.synchronize(device)
+    us = e0.elapsed_time(e1) * 1e3 / reps
+    allowed = 0
+    for pk in m["packs"]:  # keys the last token may read: its own document and the documents it links to
+        last = len(pk.lengths) - 1
+        allowed += int(pk.lengths[last]) + sum(int(pk.lengths[b_]) for a, b_ in pk.links if a == last)
+    bytes_alg = allowed * 4.0 * D * H
+    return {"B": B, "H": H, "Tk": T, "head_dim": D, "mask": m["name"], "allowed_keys": allowed, "us_per_call": us, "gpu_launches_per_call": 2,
+            "full_forward_ms_recomputed_by_the_reference": fwd_ms_full, "speedup_over_full_forward": fwd_ms_full * 1e3 / us,
+            "roofline": {"bound": "hbm", "achieved": bytes_alg / us / 1e3, "peak": hbm_gbs, "unit": "GB/s", "frac": bytes_alg / us / 1e3 / hbm_gbs,
+                         "peak_kind": peak_kind, "note": "K and V rows of the allowed keys, once; a call this short is bound by its two launches"}}
 
 
 def reference_block_mask_time(pack, device):

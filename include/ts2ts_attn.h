@@ -82,6 +82,23 @@ int ts2ts_attn_fwd(const void* q, const void* k, const void* v, const int64_t* q
                    const int32_t* q_row_ids, const int32_t* kv_col_ids, const int64_t* link_bits, int R, int W,
                    const void* plan, size_t plan_bytes, void* out, const int64_t* out_strides, float* lse, void* stream);
 
+/* Attention of ONE new token per sequence against cached keys and values (decoding with KV reuse).  The reference
+ * recomputes the whole forward for every generated token (model/generation_loop.py:90-92, model/model.py:214-237)
+ * and lists KV caching as not implemented (GENERATION_FEATURE_SPEC.md:163); this call computes the one row it needs.
+ *   q            bf16 [B,H,1,D], strides {batch, head, (ignored)}
+ *   k_cache, v_cache   bf16 [B,H,Tk,D] holding the keys / values of tokens 0 .. Tk-1, the new token's included
+ *   doc_ids, q_row_ids, kv_col_ids   int32 [B,Tk] (classes of every cached token; the query's are those at q_pos)
+ *   q_pos        device int32[B]: position of the query token, or NULL = Tk - 1
+ *   out          bf16 [B,H,1,D]; lse fp32 [B,H] natural log; a token that may read no key gets out = 0, lse = -inf
+ *   workspace    ts2ts_attn_decode_workspace_bytes(B,H,Tk,D) bytes, 256-byte aligned
+ * Keys after q_pos are never read.  No block plan is needed: the mask row is evaluated per key. */
+size_t ts2ts_attn_decode_workspace_bytes(int B, int H, int Tk, int D);
+int ts2ts_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* q_strides,
+                      const int64_t* k_strides, const int64_t* v_strides, int B, int H, int Tk, int D, float scale,
+                      const int32_t* doc_ids, const int32_t* q_row_ids, const int32_t* kv_col_ids,
+                      const int64_t* link_bits, int R, int W, const int32_t* q_pos, void* out,
+                      const int64_t* out_strides, float* lse, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Scratch size in bytes that ts2ts_attn_bwd needs. */
 size_t ts2ts_attn_bwd_workspace_bytes(int B, int H, int T, int D);
 

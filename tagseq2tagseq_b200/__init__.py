@@ -2,7 +2,8 @@
 
 Public surface:
     mask_spec   MaskSpec, mask creators with the reference's names, build_block_map (integer pre-pass)
-    attention   masked_attn (torch operator with autograd), flex_attention (drop-in signature)
+    attention   masked_attn (torch operator with autograd), masked_attn_decode (one new token against cached K / V),
+                flex_attention (drop-in signature)
     synth       seeded synthetic packs for benchmarks and tests
 """
 from .mask_spec import (BlockMap, CrossDocLinkMaskCreator, DocSpan, LinkInfo, MaskSpec, build_block_map,  # noqa: F401
@@ -11,7 +12,7 @@ from .mask_spec import (BlockMap, CrossDocLinkMaskCreator, DocSpan, LinkInfo, Ma
 
 
 def __getattr__(name):  # attention registers torch custom ops; import it lazily
-    if name in ("masked_attn", "flex_attention"):
+    if name in ("masked_attn", "masked_attn_decode", "flex_attention"):
         from . import attention
         return getattr(attention, name)
     raise AttributeError(name)

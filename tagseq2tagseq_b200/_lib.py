@@ -22,6 +22,9 @@ SYMBOLS = {
     "ts2ts_segment_ids": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "ts2ts_attn_fwd": (c_int, [c_void_p] * 3 + [POINTER(c_int64)] * 3 + [c_int] * 4 + [c_float] + [c_void_p] * 4 + [c_int] * 2
                        + [c_void_p, c_size_t, c_void_p, POINTER(c_int64), c_void_p, c_void_p]),
+    "ts2ts_attn_decode_workspace_bytes": (c_size_t, [c_int] * 4),
+    "ts2ts_attn_decode": (c_int, [c_void_p] * 3 + [POINTER(c_int64)] * 3 + [c_int] * 4 + [c_float] + [c_void_p] * 4 + [c_int] * 2
+                          + [c_void_p, c_void_p, POINTER(c_int64), c_void_p, c_void_p, c_size_t, c_void_p]),
     "ts2ts_attn_bwd_workspace_bytes": (c_size_t, [c_int] * 4),
     "ts2ts_attn_bwd": (c_int, [c_void_p] * 6 + [POINTER(c_int64)] * 5 + [c_int] * 4 + [c_float] + [c_void_p] * 4 + [c_int] * 2
                        + [c_void_p, c_size_t] + [c_void_p] * 3 + [POINTER(c_int64)] * 3 + [c_void_p, c_size_t, c_void_p]),

@@ -15,7 +15,7 @@ import torch
 from . import _lib
 from .mask_spec import MaskSpec, build_block_map
 
-__all__ = ["masked_attn", "flex_attention"]
+__all__ = ["masked_attn", "masked_attn_decode", "flex_attention"]
 
 
 def _opt_ptr(t: Optional[torch.Tensor]):
@@ -137,6 +137,66 @@ def masked_attn(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, doc_ids: torc
     if plan is None:
         plan = build_block_map(doc_ids, link_bits, q_row_ids, kv_col_ids).plan
     return _attn_fwd(q, k, v, doc_ids, link_bits, q_row_ids, kv_col_ids, plan, scale)
+
+
+@torch.library.custom_op("ts2ts::masked_attn_decode", mutates_args=())
+def _attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, doc_ids: torch.Tensor,
+                 link_bits: Optional[torch.Tensor], q_row_ids: Optional[torch.Tensor], kv_col_ids: Optional[torch.Tensor],
+                 q_pos: Optional[torch.Tensor], scale: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    B, H, Tk, D = k_cache.shape
+    q, k_cache, v_cache = _rowmajor(q), _rowmajor(k_cache), _rowmajor(v_cache)
+    out = torch.empty((B, H, 1, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H), dtype=torch.float32, device=q.device)
+    L = _lib.lib()
+    ws = torch.empty(L.ts2ts_attn_decode_workspace_bytes(B, H, Tk, D), dtype=torch.uint8, device=q.device)
+    R, W = (0, 0) if link_bits is None else (link_bits.shape[1], link_bits.shape[2])
+    with torch.cuda.device(q.device):
+        code = L.ts2ts_attn_decode(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _lib.strides3(q), _lib.strides3(k_cache), _lib.strides3(v_cache),
+            B, H, Tk, D, scale, doc_ids.data_ptr(), _opt_ptr(q_row_ids), _opt_ptr(kv_col_ids), _opt_ptr(link_bits), R, W,
+            _opt_ptr(q_pos), out.data_ptr(), _lib.strides3(out), lse.data_ptr(), ws.data_ptr(), ws.numel(),
+            torch.cuda.current_stream(q.device).cuda_stream)
+    _lib.check(code, "ts2ts_attn_decode")
+    return out, lse
+
+
+@_attn_decode.register_fake
+def _(q, k_cache, v_cache, doc_ids, link_bits, q_row_ids, kv_col_ids, q_pos, scale):
+    B, H, Tk, D = k_cache.shape
+    return q.new_empty((B, H, 1, D)), q.new_empty((B, H), dtype=torch.float32)
+
+
+def masked_attn_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, doc_ids: torch.Tensor,
+                       link_bits: Optional[torch.Tensor] = None, *, q_row_ids: Optional[torch.Tensor] = None,
+                       kv_col_ids: Optional[torch.Tensor] = None, q_pos: Optional[torch.Tensor] = None,
+                       scale: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """One decoding step with KV reuse: the attention row of the newest token of every sequence.
+
+    q        bf16 [B,H,1,D]: the new token's query
+    k_cache, v_cache   bf16 [B,H,Tk,D]: keys / values of tokens 0..Tk-1, the new token's included
+    doc_ids (and q_row_ids / kv_col_ids / link_bits as in ``masked_attn``) describe all Tk cached tokens
+    q_pos    int32 [B] position of the query token (default Tk - 1); later keys are never read
+
+    Returns (out bf16 [B,H,1,D], lse fp32 [B,H]); equal to row q_pos of ``masked_attn`` over the same Tk tokens, which
+    is what the reference obtains by recomputing the whole sequence for every generated token
+    (model/generation_loop.py:90-92).  Forward only."""
+    if not (q.is_cuda and k_cache.is_cuda and v_cache.is_cuda):
+        raise RuntimeError("ts2ts::masked_attn_decode runs on CUDA tensors only (no CPU path exists)")
+    if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16 or v_cache.dtype != torch.bfloat16:
+        raise TypeError("q, k_cache, v_cache must be bfloat16")
+    if k_cache.dim() != 4 or k_cache.shape != v_cache.shape or q.shape != (k_cache.shape[0], k_cache.shape[1], 1, k_cache.shape[3]):
+        raise ValueError("expected q [B,H,1,D] and k_cache, v_cache [B,H,Tk,D]")
+    if k_cache.shape[-1] not in (64, 128):
+        raise ValueError("head dimension must be 64 or 128")
+    if doc_ids.dtype != torch.int32 or doc_ids.shape != (k_cache.shape[0], k_cache.shape[2]):
+        raise ValueError("doc_ids must be int32 [B,Tk] matching the cache")
+    scale = 1.0 / math.sqrt(q.shape[-1]) if scale is None else float(scale)
+    if not scale > 0:
+        raise ValueError("scale must be positive")
+    cont = lambda t: None if t is None else t.contiguous()
+    if q_pos is not None and (q_pos.dtype != torch.int32 or q_pos.shape != (k_cache.shape[0],)):
+        raise ValueError("q_pos must be int32 [B]")
+    return _attn_decode(q, k_cache, v_cache, doc_ids.contiguous(), cont(link_bits), cont(q_row_ids), cont(kv_col_ids), cont(q_pos), scale)
 
 
 def flex_attention(query, key, value, score_mod=None, block_mask=None, scale=None, enable_gqa=False, return_lse=False,

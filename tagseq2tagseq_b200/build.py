@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libts2ts_attn.so")
 SELFTEST_LIB = os.path.join(HERE, "libts2ts_selftest.so")  # test-only: the bounded-wait self-test kernel
-SOURCES = ["api.cu", "block_map.cu", "link_scan.cu", "attn_fwd.cu", "attn_bwd.cu"]
+SOURCES = ["api.cu", "block_map.cu", "link_scan.cu", "attn_fwd.cu", "attn_bwd.cu", "attn_decode.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v"]
 
@@ -52,7 +52,7 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
             raise RuntimeError(f"nvcc failed on {src}:\n{res.stdout}\n{res.stderr}")
         return obj, res.stderr
 
-    with ThreadPoolExecutor(max_workers=4) as ex:
+    with ThreadPoolExecutor(max_workers=6) as ex:
         results = list(ex.map(compile_one, SOURCES))
     if verbose:
         for _, log in results:

@@ -24,6 +24,10 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
                PlanView P, MaskArgs M, void* dq, void* dk, void* dv, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv,
                void* workspace, cudaStream_t stream);
 int bwd_static_scratch(void** ptr, size_t* bytes);
+size_t decode_workspace_bytes(int B, int H, int Tk, int D);
+int launch_decode(const void* q, const void* k, const void* v, const int64_t* sq, const int64_t* sk, const int64_t* sv, int B, int H,
+                  int Tk, int D, float scale, MaskArgs M, const int32_t* q_pos, void* out, const int64_t* so, float* lse,
+                  void* workspace, cudaStream_t stream);
 
 }  // namespace ts2ts
 
@@ -148,6 +152,35 @@ int ts2ts_attn_fwd(const void* q, const void* k, const void* v, const int64_t* q
   r = launch_fwd(q, k, v, out, lse, q_strides, k_strides, v_strides, out_strides, B, H, T, D, scale, P,
                  mask_args(doc_ids, q_row_ids, kv_col_ids, link_bits, R, W), static_cast<cudaStream_t>(stream));
   if (r) return fail(r, "forward launch failed (code %d, CUDA: %s)", r, cudaGetErrorString(cudaPeekAtLastError()));
+  return 0;
+}
+
+size_t ts2ts_attn_decode_workspace_bytes(int B, int H, int Tk, int D) {
+  if (B <= 0 || H <= 0 || Tk <= 0 || Tk > kMaxT || (D != 64 && D != 128)) return 0;
+  return decode_workspace_bytes(B, H, Tk, D);
+}
+
+int ts2ts_attn_decode(const void* q, const void* k_cache, const void* v_cache, const int64_t* q_strides, const int64_t* k_strides,
+                      const int64_t* v_strides, int B, int H, int Tk, int D, float scale, const int32_t* doc_ids,
+                      const int32_t* q_row_ids, const int32_t* kv_col_ids, const int64_t* link_bits, int R, int W,
+                      const int32_t* q_pos, void* out, const int64_t* out_strides, float* lse, void* workspace,
+                      size_t workspace_bytes, void* stream) {
+  int r;
+  if ((r = check_shape(B, H, Tk, D))) return r;
+  if (B > 65535 || H > 65535) return fail(-1, "B and H must not exceed 65535 for the decoding call");
+  if (!(scale > 0.f)) return fail(-8, "scale must be positive");
+  if ((r = check_tensor("q", q, q_strides)) || (r = check_tensor("k_cache", k_cache, k_strides)) ||
+      (r = check_tensor("v_cache", v_cache, v_strides)) || (r = check_tensor("out", out, out_strides)))
+    return r;
+  if (lse == nullptr) return fail(-3, "lse: null pointer");
+  if ((r = check_mask(doc_ids, link_bits, R, W))) return r;
+  if (workspace == nullptr || !aligned(workspace, 256)) return fail(-9, "workspace must be a 256-byte aligned device buffer");
+  if (workspace_bytes < decode_workspace_bytes(B, H, Tk, D))
+    return fail(-9, "workspace too small: %zu < %zu", workspace_bytes, decode_workspace_bytes(B, H, Tk, D));
+  r = launch_decode(q, k_cache, v_cache, q_strides, k_strides, v_strides, B, H, Tk, D, scale,
+                    mask_args(doc_ids, q_row_ids, kv_col_ids, link_bits, R, W), q_pos, out, out_strides, lse, workspace,
+                    static_cast<cudaStream_t>(stream));
+  if (r) return fail(r, "decode launch failed (code %d, CUDA: %s)", r, cudaGetErrorString(cudaPeekAtLastError()));
   return 0;
 }
 

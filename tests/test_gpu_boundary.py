@@ -174,3 +174,36 @@ def test_segment_ids_filled_on_the_device_and_reference_format_adapter():
     got = om.class_mask_dense(spec.doc_ids[0].cpu().numpy(), spec.q_row_ids[0].cpu().numpy(), spec.kv_col_ids[0].cpu().numpy(),
                               spec.link_bits[0].cpu().numpy())
     assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("d,t,p", [(128, 1000, 0.25), (64, 777, 0.0), (128, 129, 0.4)])
+def test_decode_step_with_cached_keys_equals_the_row_of_the_full_forward(d, t, p):
+    """One new token against cached K / V: must equal the corresponding row of the whole-sequence attention, which is
+    what the reference recomputes for every generated token (model/generation_loop.py:90-92).  Checked against the
+    fp32 oracle and against this package's own full forward, at the last position and at an inner one (q_pos)."""
+    from tagseq2tagseq_b200 import build_block_map, synth
+    from tagseq2tagseq_b200.attention import masked_attn, masked_attn_decode
+    dev = torch.device("cuda")
+    pack = synth.make_pack(31, t, 60, 4, 300, p_link=p)
+    doc = torch.from_numpy(pack.doc_ids)[None].to(dev).expand(2, -1).contiguous()
+    link = None if pack.link_bits is None else torch.from_numpy(pack.link_bits)[None].to(dev).expand(2, -1, -1).contiguous()
+    dense = torch.from_numpy(om.class_mask_dense(pack.doc_ids, None, None, pack.link_bits))[None]
+    g = torch.Generator().manual_seed(5)
+    q, k, v, do = (torch.randn(2, 3, t, d, generator=g).bfloat16() for _ in range(4))
+    full, full_lse = masked_attn(q.to(dev), k.to(dev), v.to(dev), doc, link, plan=build_block_map(doc, link).plan)
+    for pos in (t - 1, t // 2):
+        q_pos = None if pos == t - 1 else torch.full((2,), pos, dtype=torch.int32, device=dev)
+        out, lse = masked_attn_decode(q[:, :, pos:pos + 1].to(dev), k.to(dev), v.to(dev), doc, link, q_pos=q_pos)
+        assert out.shape == (2, 3, 1, d) and lse.shape == (2, 3)
+        for b in range(2):
+            ro, rl = oattn.forward_backward(q[b:b + 1], k[b:b + 1], v[b:b + 1], dense, do[b:b + 1])[:2]
+            assert (out[b, :, 0].float().cpu() - ro[0, :, pos]).abs().max().item() <= O_TOL
+            assert (lse[b].cpu() - rl[0, :, pos]).abs().max().item() <= LSE_TOL
+        assert (out[:, :, 0].float() - full[:, :, pos].float()).abs().max().item() <= O_TOL
+        assert (lse - full_lse[:, :, pos]).abs().max().item() <= LSE_TOL
+    # a strided cache (heads interleaved as in a fused projection) is read in place
+    kc = k.permute(0, 2, 1, 3).contiguous().to(dev).permute(0, 2, 1, 3)
+    vc = v.permute(0, 2, 1, 3).contiguous().to(dev).permute(0, 2, 1, 3)
+    out2, _ = masked_attn_decode(q[:, :, t - 1:t].to(dev), kc, vc, doc, link)
+    out1, _ = masked_attn_decode(q[:, :, t - 1:t].to(dev), k.to(dev), v.to(dev), doc, link)
+    assert torch.equal(out1, out2)
