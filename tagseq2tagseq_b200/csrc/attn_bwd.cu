@@ -71,6 +71,12 @@ constexpr int kRunSlotsB = 4;     // runs of a partial query tile that the produ
 #ifndef TS2TS_BWD_ELECT
 #define TS2TS_BWD_ELECT 1
 #endif
+#ifndef TS2TS_BWD_DQ_FIRST
+#define TS2TS_BWD_DQ_FIRST 1
+#endif
+#ifndef TS2TS_BWD_SPLIT_ST
+#define TS2TS_BWD_SPLIT_ST 1  // S^T of the next tile in two 64-query halves, the first right behind the first half of dV / dK
+#endif
 
 template <int D>
 struct BwdSmem {
@@ -241,7 +247,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   uint64_t& bar_g = bars[8];           // gradient MMAs of the tile completed (dQ^T readable)
   uint64_t& bar_dqr = bars[9];         // dQ^T read out of tensor memory
   uint64_t& bar_epi = bars[10];
-  uint64_t& bar_s = bars[12];          // S^T of the tile is in tensor memory (dP^T may still be running)
+  uint64_t* bar_s = bars + 12;         // [2] S^T of a 64-query half of the tile is in tensor memory (dP^T may still be running)
   uint32_t& tmem_slot = *reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_ptr = reinterpret_cast<volatile int*>(reinterpret_cast<uint8_t*>(bars + 16) + 4);
   int* abort_w = const_cast<int*>(abort_ptr);
@@ -296,7 +302,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
     mbar_init(&bar_g, 1);
     mbar_init(&bar_dqr, kTile);
     mbar_init(&bar_epi, 2 * kTile);
-    mbar_init(&bar_s, 1);
+    mbar_init(&bar_s[0], 1);
+    mbar_init(&bar_s[1], 1);
     fence_mbar_init();
   }
   __syncthreads();
@@ -376,7 +383,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
           mma_ss2(tST, k_kmaj + off, hi, q_kmaj + stage + off, hi, idesc_st, kk > 0);
         }
-        mma_commit(&bar_s);
+        mma_commit(&bar_s[0]);
+        mma_commit(&bar_s[1]);
+      };
+      constexpr uint32_t idesc_st64 = make_idesc_bf16(128, 64, false, false);
+      auto issue_st_half = [&](uint32_t stage, int hq) {  // S^T[:, 64 hq, +64) = K Q[64 hq, +64)^T  (N = 64)
+        const uint32_t rows = (uint32_t)hq * (kSubQ * 128) >> 4;  // 64 query rows x 128 B of the K-major Q tile
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t off = ((kk >> 2) * 16384 + (kk & 3) * 32) >> 4;
+          mma_ss2(tST + 64 * hq, k_kmaj + off, hi, q_kmaj + stage + rows + off, hi, idesc_st64, kk > 0);
+        }
+        mma_commit(&bar_s[hq]);
       };
       auto issue_dpt = [&]() {  // dP^T = V dO^T
 #pragma unroll
@@ -422,6 +440,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #pragma unroll
           for (int kk = 0; kk < kSubQ / 16; ++kk)  // dK += dS^T Q
             mma_ts2(tDK, tST + 64 * s + (kk >> 1) * 32 + 16 + (kk & 1) * 8, q_mn + stage + half_rows + kk * 128, hi, idesc_g, kk > 0 ? 1u : acc);
+#if TS2TS_BWD_SPLIT_ST && !defined(TS2TS_STRICT_ORDER)
+          if (s == 0 && more) {
+            // The first half of S^T(i+1) overwrites the P^T / dS^T columns of half 0 of tile i, whose readers were
+            // issued just above: it runs while the compute warps still work on half 1, so that their exponentials of
+            // tile i+1 can start the moment they are done with tile i.
+            if (!mbar_wait(&bar_q_full[st ^ 1], ((i + 1) >> 1) & 1, abort_w, 22)) { fail = true; break; }
+            tc_fence_after();
+            issue_st_half(next, 0);
+          }
+#endif
         }
         if (fail) break;
         mma_commit(&bar_gd);
@@ -435,14 +463,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           issue_st(next);
         }
 #else
+#if TS2TS_BWD_SPLIT_ST && TS2TS_BWD_DQ_FIRST
+        issue_dqt();  // its read-out by the reduction warps then overlaps the second half of S^T(i+1)
+        TRACE(0, i, 5);
+#endif
         if (more) {
+#if TS2TS_BWD_SPLIT_ST
+          issue_st_half(next, 1);
+#else
           if (!mbar_wait(&bar_q_full[st ^ 1], ((i + 1) >> 1) & 1, abort_w, 22)) break;
           tc_fence_after();
           issue_st(next);
+#endif
           TRACE(0, i, 0);
         }
+#if !(TS2TS_BWD_SPLIT_ST && TS2TS_BWD_DQ_FIRST)
         issue_dqt();
         TRACE(0, i, 5);
+#endif
 #endif
         if (more) {
           if (!mbar_wait(&bar_dqr, i & 1, abort_w, 23)) break;  // dQ^T(i) read out of the columns dP^T(i+1) overwrites
@@ -521,8 +559,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
         }
       }
       if (masked) BTRACE_ACC(0); else BTRACE_ACC(1);
-      // ---- phase 1: exponentials, as soon as S^T is complete
-      if (!(ok = mbar_wait(&bar_s, i & 1, abort_w, 35))) break;
+      // ---- phase 1: exponentials, as soon as the half of S^T is complete
+      if (!(ok = mbar_wait(&bar_s[0], i & 1, abort_w, 35))) break;
       tc_fence_after();
       BTRACE_ACC(2);
       if (tid == 0) TRACE(1, i, 0);
@@ -537,6 +575,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
 #pragma unroll
         for (int s = 0; s < 2; ++s) {
 #if !TS2TS_BWD_LD2
+          if (s == 1) {
+            if (!(ok = mbar_wait(&bar_s[1], i & 1, abort_w, 36))) break;
+            tc_fence_after();
+          }
           tmem_ld32(tST + lane_base + 64 * s + 32 * half, sv[s]);
           tmem_ld_wait();
 #endif
@@ -544,6 +586,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
           tmem_st16(tST + lane_base + 64 * s + 32 * half, pk[s]);
         }
       }
+      if (!ok) break;
       if (tid == 0) TRACE(1, i, 1);
       BTRACE_ACC(3);
       // ---- phase 2: dS^T, once dP^T is complete
