@@ -116,16 +116,17 @@ __global__ void __launch_bounds__(128) lists_kernel(PlanView P, int transposed, 
 }
 
 // Forward work items are pairs of adjacent q tiles (2p, 2p+1) that share one stream of K/V tiles: count the kv
-// tiles at least one of the two reads.  One thread per (pair, b).
+// tiles at least one of the two reads.  One warp per (pair, b).
 __global__ void __launch_bounds__(128) pair_count_kernel(PlanView P) {
-  const int pr = blockIdx.x * blockDim.x + threadIdx.x, b = blockIdx.y;
+  const int pr = blockIdx.x * 4 + (threadIdx.x >> 5), b = blockIdx.y, lane = threadIdx.x & 31;
   const int NP = (P.NB + 1) / 2;
   if (pr >= NP) return;
   const uint8_t* s0 = P.state + ((size_t)b * P.NB + 2 * pr) * P.NB;
   const uint8_t* s1 = (2 * pr + 1 < P.NB) ? s0 + P.NB : s0;
   int n = 0;
-  for (int kb = 0; kb <= min(2 * pr + 1, P.NB - 1); ++kb) n += (s0[kb] | s1[kb]) != kSkip;
-  P.pair_cnt[(size_t)b * NP + pr] = n;
+  for (int kb = lane; kb <= min(2 * pr + 1, P.NB - 1); kb += 32) n += (s0[kb] | s1[kb]) != kSkip;
+  for (int sh = 16; sh > 0; sh >>= 1) n += __shfl_xor_sync(0xffffffffu, n, sh);
+  if (lane == 0) P.pair_cnt[(size_t)b * NP + pr] = n;
 }
 
 // Heaviest-first order inside each batch element: rank by descending count, ties by index.
@@ -194,7 +195,7 @@ cudaError_t launch_block_map(PlanView P, MaskArgs M, uint8_t* state_out, int32_t
   state_kernel<<<dim3((P.NB + 127) / 128, P.NB, P.B), 128, 0, stream>>>(P, M);
   lists_kernel<<<dim3((P.NB + 3) / 4, P.B), 128, 0, stream>>>(P, 0, kv_cnt, kv_idx, full_cnt, full_idx);
   lists_kernel<<<dim3((P.NB + 3) / 4, P.B), 128, 0, stream>>>(P, 1, q_cnt, q_idx, full_q_cnt, full_q_idx);
-  pair_count_kernel<<<dim3(((P.NB + 1) / 2 + 127) / 128, P.B), 128, 0, stream>>>(P);
+  pair_count_kernel<<<dim3(((P.NB + 1) / 2 + 3) / 4, P.B), 128, 0, stream>>>(P);
   order_kernel<<<dim3((P.NB + 255) / 256, P.B, 3), 256, 0, stream>>>(P);
   int link_t_rows = 0;
   if (M.link != nullptr && M.R > 0 && M.R <= kLinkTMaxRows && 64 * M.W <= kLinkTMaxCols) {
