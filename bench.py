@@ -537,7 +537,7 @@ def run_train(args, rank, world, device, which: str, steps: int, warmup: int, bo
     from tagseq2tagseq_b200.replicas import aggregate, rank_seed, schedule_packs, tile_cost
     from tagseq2tagseq_b200.train_step import TrainStep, config4, config5, train_flops_per_step
     cfg, t_len, base = (config4(), 16384, 1004) if which == "train4" else (config5(), 32768, 1005)
-    ts = TrainStep(cfg, device, world)
+    ts = TrainStep(cfg, device, world, bucket_cap_mb=args.bucket_mb)
     n_packs = 4  # steps in the pool
     make = (lambda sd: synth.config2_pack(sd)) if which == "train4" else (lambda sd: synth.config5_pack(sd))
     pool = [make(rank_seed(base, r, i)) for i in range(n_packs) for r in range(world)]
@@ -615,7 +615,7 @@ def run_train(args, rank, world, device, which: str, steps: int, warmup: int, bo
            "model": f"{cfg.n_layers}L d{cfg.d_model} {cfg.n_heads}h hd{cfg.head_dim} swiglu{cfg.mlp_hidden} V{cfg.vocab}",
            "seq_len": t_len, "global_batch_tokens": t_len * world, "parallelism": f"ddp{world}", "pack_schedule": first,
            "optimizer": "fused AdamW (fp32 params, bf16 autocast)",
-           "gradient_allreduce": "none (1 GPU)" if world == 1 else f"NCCL, {'bf16-compressed' if ts.bf16_grads else 'fp32'} buckets, {ts.grad_bytes_per_step / 1e9:.2f} GB per rank per step",
+           "gradient_allreduce": "none (1 GPU)" if world == 1 else f"NCCL, {'bf16-compressed' if ts.bf16_grads else 'fp32'} buckets of {args.bucket_mb} MB (fp32 size), {ts.grad_bytes_per_step / 1e9:.2f} GB per rank per step",
            "peak_kind": kind}
     out.update(main)
     if both_schedules and world > 1 and not args.no_balance:
@@ -911,6 +911,7 @@ def main():
                     help="ours: this package's CUDA path.  reference: the reference's CPU path on a bounded sample.  "
                          "flex_gpu: PyTorch FlexAttention (the reference's GPU path) on the same inputs, single GPU.")
     ap.add_argument("--no-balance", action="store_true", help="training step: keep the seed order of packs instead of the density-aware schedule")
+    ap.add_argument("--bucket-mb", type=int, default=256, help="training step: DDP bucket size in MB (the reference uses 256, main.py:414)")
     ap.add_argument("--no-train", action="store_true", help="skip the short training-step measurement appended to the 32k line")
     ap.add_argument("--workload", default="32k", choices=["32k", "16k", "train4", "train5"],
                     help="32k: the headline mask sweep (default).  16k: B=1, T=16384, H=16, cross_doc_link p=0.15 "

@@ -55,6 +55,7 @@ struct BwdParams {
   __nv_bfloat16* dv;
   int64_t dk_s[3], dv_s[3];
   int H, Tp;
+  int head_group;        // heads whose CTAs are interleaved in the launch order
   float scale, scale_log2;
   TS2TS_BWD_TRACE_FIELDS
 };
@@ -267,9 +268,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant_
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const PlanView& P = p.plan;
   const int NB = P.NB;
-  const int rank = blockIdx.x % NB;
-  const int bh = blockIdx.x / NB;
-  const int h = bh % p.H, b = bh / p.H;
+  // Launch order (the hardware starts CTAs by ascending blockIdx): batch elements one after the other; inside one,
+  // groups of G heads; inside a group all heads' heaviest kv tiles first, then their second heaviest, and so on.  The
+  // group bounds the Q / dO working set that has to stay in L2, and the long CTAs of the last group still start well
+  // before the end of the launch instead of running alone at its tail.
+  const int per_b = p.H * NB, G = p.head_group;
+  const int b = blockIdx.x / per_b;
+  const int r1 = blockIdx.x - b * per_b;
+  const int grp = r1 / (G * NB);
+  const int r2 = r1 - grp * G * NB;
+  const int gsize = min(G, p.H - grp * G);
+  const int rank = r2 / gsize;
+  const int h = grp * G + (r2 - rank * gsize);
   const int kb = min(max(P.bwd_order[(size_t)b * NB + rank], 0), NB - 1);
   const int n = min(max(P.bwd_cnt[(size_t)b * NB + kb], 0), NB);
   const int32_t* list = P.bwd_idx + ((size_t)b * NB + kb) * NB;
@@ -826,6 +836,11 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   for (int i = 0; i < 3; ++i) { p.dk_s[i] = sdk[i]; p.dv_s[i] = sdv[i]; }
   p.H = H; p.Tp = Tp; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  {  // heads per group: their Q and dO (2 x T x D bf16 each) should fit in about half of the 126 MB L2
+    const long long qdo_bytes = 4ll * T * D;
+    long long g = (64ll << 20) / (qdo_bytes > 0 ? qdo_bytes : 1);
+    p.head_group = (int)(g < 1 ? 1 : (g > H ? H : g));
+  }
   BTRACE_ATTACH(p, stream);
   {
     ProfileScope timed(1, stream);

@@ -125,7 +125,7 @@ class TrainStep:
     halves the bytes on NVLink; the parameters and the optimizer state stay fp32."""
 
     def __init__(self, cfg: LMConfig, device: torch.device, world: int = 1, lr: float = 3e-4, seed: int = 0,
-                 bf16_grads: bool = True):
+                 bf16_grads: bool = True, bucket_cap_mb: int = 256):
         torch.manual_seed(seed)  # identical initial weights on every rank
         self.cfg, self.device, self.world = cfg, device, world
         model = DecoderLM(cfg).to(device)
@@ -133,7 +133,7 @@ class TrainStep:
         self.bf16_grads = bool(bf16_grads and world > 1)
         if world > 1:
             self.model = torch.nn.parallel.DistributedDataParallel(
-                model, device_ids=[device.index], static_graph=True, find_unused_parameters=False, bucket_cap_mb=256,
+                model, device_ids=[device.index], static_graph=True, find_unused_parameters=False, bucket_cap_mb=bucket_cap_mb,
                 gradient_as_bucket_view=True)
             if self.bf16_grads:
                 from torch.distributed.algorithms.ddp_comm_hooks import default_hooks
