@@ -126,3 +126,25 @@ def test_fuzz_random_classes_and_ragged_lengths(seed):
     st = obm.block_states(om.class_mask_dense(doc, row, col, link))
     assert np.array_equal(bm.state[0].cpu().numpy(), st)
     _check_lists(bm, st)
+
+
+def test_tile_cost_counts_the_non_skipped_tiles_and_orders_packs_like_the_exact_pair_count():
+    """The cost the density-aware schedule uses: non-skipped 128 x 128 tiles from the pre-pass (one read-back per pack),
+    equal to the oracle's count, and ranking heavy-tailed packs like the exact number of unmasked pairs does."""
+    from oracle import block_map as obm
+    from tagseq2tagseq_b200 import synth
+    from tagseq2tagseq_b200.replicas import schedule_packs, step_time_model, tile_cost
+    dev = torch.device("cuda")
+    packs = [synth.make_pack(600 + i, 4096, 150, 16, 2048, p_link=0.15, heavy_frac=0.05, heavy_lo=1024, heavy_hi=2048) for i in range(8)]
+    costs = []
+    for pk in packs:
+        doc = torch.from_numpy(pk.doc_ids)[None].to(dev)
+        link = torch.from_numpy(pk.link_bits)[None].to(dev)
+        c = tile_cost(doc, link)
+        dense = om.class_mask_dense(pk.doc_ids, None, None, pk.link_bits)
+        assert c == int((obm.block_states(dense) != obm.SKIP).sum())
+        costs.append(float(c))
+    exact = [float(pk.unmasked_pairs()) for pk in packs]
+    sched = schedule_packs(costs, 2)
+    naive = [[0, 1], [2, 3], [4, 5], [6, 7]]
+    assert step_time_model(exact, sched) <= step_time_model(exact, naive)  # tile counts balance the true cost too
