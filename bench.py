@@ -161,8 +161,8 @@ def run_ours(args, rank, world, device):
             bm = build_block_map(m["doc"], m["link"])
             out, lse = _attn_fwd(q, k, v, m["doc"], m["link"], None, None, bm.plan, scale)
             _attn_bwd(q, k, v, out, do, lse, m["doc"], m["link"], None, None, bm.plan, scale)
-            # pre-pass (runs, state, 2 x lists, pair counts, orders, stamp; + transposed links), forward, backward (prep, main, convert)
-            launches[0] += 7 + (1 if m["link"] is not None else 0) + 1 + 3
+            # pre-pass (runs, state, lists, pair counts, orders; + transposed links), forward, backward (prep, main, convert)
+            launches[0] += 5 + (1 if m["link"] is not None else 0) + 1 + 3
         return bm
 
     def barrier():

@@ -85,8 +85,15 @@ __global__ void __launch_bounds__(128) state_kernel(PlanView P, MaskArgs M) {
 // One warp per line.  transposed == 0: line = q tile, scan kv tiles; 1: line = kv tile, scan q tiles.
 // Writes the merged list used by the kernels and, when given, the separate partial / full lists in the
 // BlockMask convention (ascending, entries past the count = -1).
-__global__ void __launch_bounds__(128) lists_kernel(PlanView P, int transposed, int32_t* part_cnt, int32_t* part_idx,
-                                                    int32_t* full_cnt, int32_t* full_idx) {
+struct ListOutputs {
+  int32_t *part_cnt, *part_idx, *full_cnt, *full_idx;
+};
+__global__ void __launch_bounds__(128) lists_kernel(PlanView P, ListOutputs fwd_out, ListOutputs bwd_out) {
+  const int transposed = blockIdx.z;  // 0: line = q tile, scan kv tiles; 1: line = kv tile, scan q tiles
+  int32_t* part_cnt = transposed ? bwd_out.part_cnt : fwd_out.part_cnt;
+  int32_t* part_idx = transposed ? bwd_out.part_idx : fwd_out.part_idx;
+  int32_t* full_cnt = transposed ? bwd_out.full_cnt : fwd_out.full_cnt;
+  int32_t* full_idx = transposed ? bwd_out.full_idx : fwd_out.full_idx;
   const int line = blockIdx.x * 4 + (threadIdx.x >> 5), b = blockIdx.y, lane = threadIdx.x & 31;
   if (line >= P.NB) return;
   const size_t lb = (size_t)b * P.NB + line;
@@ -131,9 +138,15 @@ __global__ void __launch_bounds__(128) pair_count_kernel(PlanView P) {
 
 // Heaviest-first order inside each batch element: rank by descending count, ties by index.
 // which = 0: q tiles by fwd_cnt, 1: kv tiles by bwd_cnt, 2: q-tile pairs by pair_cnt.
-__global__ void __launch_bounds__(256) order_kernel(PlanView P) {
+__global__ void __launch_bounds__(256) order_kernel(PlanView P, int link_t_rows) {
   const int b = blockIdx.y, which = blockIdx.z;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i == 0 && b == 0 && which == 0) {  // this is the last launch of the pre-pass: stamp the plan (see plan.h)
+    P.status[kStampMagic] = kPlanMagic;
+    P.status[kStampB] = P.B;
+    P.status[kStampT] = P.T;
+    P.status[kLinkTRows] = link_t_rows;
+  }
   const int n = which == 2 ? (P.NB + 1) / 2 : P.NB;
   if (i >= n) return;
   const int32_t* cnt = (which == 2 ? P.pair_cnt : which == 1 ? P.bwd_cnt : P.fwd_cnt) + (size_t)b * n;
@@ -156,13 +169,6 @@ __global__ void __launch_bounds__(128) link_transpose_kernel(PlanView P, MaskArg
   for (int r = 64 * w; r < min(64 * w + 64, M.R); ++r)
     out |= ((static_cast<unsigned long long>(link_b[(size_t)r * M.W + (c >> 6)]) >> (c & 63)) & 1ull) << (r - 64 * w);
   P.link_t[((size_t)b * kLinkTMaxCols + c) * kLinkTWords + w] = out;
-}
-
-__global__ void stamp_kernel(PlanView P, int link_t_rows) {
-  P.status[kStampMagic] = kPlanMagic;
-  P.status[kStampB] = P.B;
-  P.status[kStampT] = P.T;
-  P.status[kLinkTRows] = link_t_rows;
 }
 
 // Per-token ids from a sorted table of segments: token t gets ids[j] for bounds[j] <= t < bounds[j + 1], and -1 before
@@ -193,16 +199,15 @@ cudaError_t launch_block_map(PlanView P, MaskArgs M, uint8_t* state_out, int32_t
   cudaMemsetAsync(P.status, 0, 64 * sizeof(int32_t), stream);
   runs_kernel<<<dim3(P.NB, P.B), 128, 0, stream>>>(P, M);
   state_kernel<<<dim3((P.NB + 127) / 128, P.NB, P.B), 128, 0, stream>>>(P, M);
-  lists_kernel<<<dim3((P.NB + 3) / 4, P.B), 128, 0, stream>>>(P, 0, kv_cnt, kv_idx, full_cnt, full_idx);
-  lists_kernel<<<dim3((P.NB + 3) / 4, P.B), 128, 0, stream>>>(P, 1, q_cnt, q_idx, full_q_cnt, full_q_idx);
+  lists_kernel<<<dim3((P.NB + 3) / 4, P.B, 2), 128, 0, stream>>>(P, ListOutputs{kv_cnt, kv_idx, full_cnt, full_idx},
+                                                                  ListOutputs{q_cnt, q_idx, full_q_cnt, full_q_idx});
   pair_count_kernel<<<dim3(((P.NB + 1) / 2 + 3) / 4, P.B), 128, 0, stream>>>(P);
-  order_kernel<<<dim3((P.NB + 255) / 256, P.B, 3), 256, 0, stream>>>(P);
   int link_t_rows = 0;
   if (M.link != nullptr && M.R > 0 && M.R <= kLinkTMaxRows && 64 * M.W <= kLinkTMaxCols) {
     link_t_rows = M.R;
     link_transpose_kernel<<<dim3((64 * M.W + 127) / 128, (M.R + 63) / 64, P.B), 128, 0, stream>>>(P, M);
   }
-  stamp_kernel<<<1, 1, 0, stream>>>(P, link_t_rows);
+  order_kernel<<<dim3((P.NB + 255) / 256, P.B, 3), 256, 0, stream>>>(P, link_t_rows);
   if (state_out)
     cudaMemcpyAsync(state_out, P.state, (size_t)P.B * P.NB * P.NB, cudaMemcpyDeviceToDevice, stream);
   return cudaGetLastError();
