@@ -60,6 +60,15 @@ def measured_peaks():
     return 1590.0, 6650.0, "fallback"
 
 
+def sustained_peak():
+    """Dense bf16 rate of a seconds-long GEMM loop under the power cap (the ruler for a kernel timed inside a long loop)."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f).get("bf16_tflops_sustained")
+    return 1400.0
+
+
 class ClockSampler:
     """SM clock and throttle reasons sampled every 50 ms while the timed region runs, read-only through NVML in a
     background thread (spawning nvidia-smi inside the timed region was measured to stall the GPU for tens of
@@ -326,6 +335,8 @@ def run_ours(args, rank, world, device):
         "clocks": clocks.result,
         "roofline": {"bound": "tensor", "kernel": "attn_bwd_kernel<128>", "achieved": achieved, "peak": peak_tf, "unit": "TFLOP/s",
                      "frac": achieved / peak_tf, "peak_kind": peak_kind + " (burst)", "avg_launch_ms": bwd_ms,
+                     # the launches are timed inside the seconds-long loop, at the clock the power cap leaves
+                     "peak_sustained": sustained_peak(), "frac_of_sustained": achieved / sustained_peak(),
                      "algorithmic_flops_per_launch": bwd_flops,
                      # dram read + write bytes per launch from the recorded ncu capture, scaled by B*H*T to this workload
                      "traffic": None if traffic is None else traffic["bwd_bytes_per_bht"] * (B * H * T),

@@ -1,4 +1,4 @@
-"""ctypes binding of libts2ts_attn.so (declarations: include/ts2ts_attn.h).
+"""ctypes binding of libts2ts_attn.so (declarations: include/ts2ts_attn.h and include/ts2ts_lm.h).
 
 There is no fallback: if the library is missing and cannot be built, importing the
 attention entry points raises.  Nothing here computes on the CPU.
@@ -13,7 +13,7 @@ from . import build as _build
 
 _LIB = None
 
-# name -> (restype, argtypes); must list every symbol include/ts2ts_attn.h declares
+# name -> (restype, argtypes); must list every symbol include/ts2ts_attn.h and include/ts2ts_lm.h declare
 SYMBOLS = {
     "ts2ts_version": (c_int, []),
     "ts2ts_last_error_string": (c_char_p, []),
@@ -37,6 +37,15 @@ SYMBOLS = {
     "ts2ts_read_status": (c_int, [c_void_p, c_void_p, POINTER(c_int32)]),
     "ts2ts_profile_enable": (c_int, [c_int]),
     "ts2ts_profile_last_ms": (c_int, [c_int, POINTER(c_float)]),
+    # include/ts2ts_lm.h
+    "ts2ts_add_rmsnorm_fwd": (c_int, [c_void_p] * 6 + [c_int64, c_int, c_float, c_void_p]),
+    "ts2ts_add_rmsnorm_bwd_workspace_bytes": (c_size_t, [c_int64, c_int]),
+    "ts2ts_add_rmsnorm_bwd": (c_int, [c_void_p] * 9 + [c_size_t, c_int64, c_int, c_void_p]),
+    "ts2ts_rope_qk_inplace": (c_int, [c_void_p] * 3 + [c_int] * 4 + [c_float, c_void_p]),
+    "ts2ts_swiglu_fwd": (c_int, [c_void_p] * 2 + [c_int64, c_int, c_void_p]),
+    "ts2ts_swiglu_bwd": (c_int, [c_void_p] * 3 + [c_int64, c_int, c_void_p]),
+    "ts2ts_ce_fwd": (c_int, [c_void_p] * 4 + [c_int64, c_int, c_void_p]),
+    "ts2ts_ce_bwd": (c_int, [c_void_p] * 4 + [c_float, c_int64, c_int, c_void_p]),
 }
 
 

@@ -17,7 +17,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libts2ts_attn.so")
 SELFTEST_LIB = os.path.join(HERE, "libts2ts_selftest.so")  # test-only: the bounded-wait self-test kernel
-SOURCES = ["api.cu", "block_map.cu", "link_scan.cu", "attn_fwd.cu", "attn_bwd.cu", "attn_decode.cu"]
+SOURCES = ["api.cu", "block_map.cu", "link_scan.cu", "attn_fwd.cu", "attn_bwd.cu", "attn_decode.cu", "lm_fused.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--use_fast_math", "-Xptxas", "-v"]
 
@@ -33,7 +33,7 @@ def _stale() -> bool:
     if not os.path.exists(LIB) or not os.path.exists(SELFTEST_LIB):
         return True
     t = os.path.getmtime(LIB)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "ts2ts_attn.h")]
+    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", h) for h in ("ts2ts_attn.h", "ts2ts_lm.h")]
     return any(os.path.getmtime(d) > t for d in deps)
 
 

@@ -1,6 +1,7 @@
 // extern "C" surface of libts2ts_attn.so: argument checks, then kernel launches on the caller's stream.
 // Declarations and the contract of every entry point are in include/ts2ts_attn.h.
 #include "../../include/ts2ts_attn.h"
+#include "../../include/ts2ts_lm.h"
 
 #include <cuda_runtime.h>
 #include <stdarg.h>
@@ -24,6 +25,17 @@ int launch_bwd(const void* q, const void* k, const void* v, const void* out, con
                PlanView P, MaskArgs M, void* dq, void* dk, void* dv, const int64_t* sdq, const int64_t* sdk, const int64_t* sdv,
                void* workspace, cudaStream_t stream);
 int bwd_static_scratch(void** ptr, size_t* bytes);
+cudaError_t launch_add_rmsnorm_fwd(const float* x_in, const void* a, const float* w, float* x_out, void* h, float* rstd, int N, int C,
+                                   float eps, cudaStream_t stream);
+cudaError_t launch_add_rmsnorm_bwd(const void* dh, const float* dx_up, const float* x, const float* w, const float* rstd, float* dx,
+                                   void* da, float* dw, float* dw_part, int N, int C, cudaStream_t stream);
+int add_rmsnorm_bwd_blocks(int64_t N, int C);
+cudaError_t launch_rope_qk(void* qkv, const float* cs, const float* sn, int B, int T, int H, int D, float sign, cudaStream_t stream);
+cudaError_t launch_swiglu_fwd(const void* gu, void* act, int64_t N, int F, cudaStream_t stream);
+cudaError_t launch_swiglu_bwd(const void* gu, const void* dact, void* dgu, int64_t N, int F, cudaStream_t stream);
+cudaError_t launch_ce_fwd(const void* logits, const int64_t* target, float* lse, float* loss, int N, int V, cudaStream_t stream);
+cudaError_t launch_ce_bwd(void* logits, const int64_t* target, const float* lse, const float* gscale, float inv_n, int N, int V,
+                          cudaStream_t stream);
 size_t decode_workspace_bytes(int B, int H, int Tk, int D);
 int launch_decode(const void* q, const void* k, const void* v, const int64_t* sq, const int64_t* sk, const int64_t* sv, int B, int H,
                   int Tk, int D, float scale, MaskArgs M, const int32_t* q_pos, void* out, const int64_t* so, float* lse,
@@ -304,3 +316,87 @@ int ts2ts_profile_last_ms(int which, float* ms) {
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------------ decoder-layer pieces (ts2ts_lm.h)
+namespace {
+constexpr int64_t kMaxRows = int64_t(1) << 30;
+int check_rows(int64_t N) { return (N <= 0 || N > kMaxRows) ? fail(-1, "N must be in 1..2^30 (got %lld)", (long long)N) : 0; }
+int launched(cudaError_t e, const char* what) { return e == cudaSuccess ? 0 : fail(-50, "%s launch failed: %s", what, cudaGetErrorString(e)); }
+}  // namespace
+
+int ts2ts_add_rmsnorm_fwd(const float* x_in, const void* a, const float* w, float* x_out, void* h, float* rstd, int64_t N, int C,
+                          float eps, void* stream) {
+  int r;
+  if ((r = check_rows(N))) return r;
+  if (C < 4 || C > 16384 || C % 4) return fail(-2, "C must be a multiple of 4 in 4..16384 (got %d)", C);
+  if (!(eps >= 0.f)) return fail(-8, "eps must not be negative");
+  if (!x_in || !w || !x_out || !h || !rstd) return fail(-3, "add_rmsnorm_fwd: null pointer");
+  if (!aligned(x_in, 16) || !aligned(x_out, 16) || !aligned(w, 16) || !aligned(h, 8) || (a && !aligned(a, 8)))
+    return fail(-5, "add_rmsnorm_fwd: misaligned pointer");
+  return launched(launch_add_rmsnorm_fwd(x_in, a, w, x_out, h, rstd, (int)N, C, eps, static_cast<cudaStream_t>(stream)), "add_rmsnorm_fwd");
+}
+
+size_t ts2ts_add_rmsnorm_bwd_workspace_bytes(int64_t N, int C) {
+  if (N <= 0 || N > kMaxRows || C < 4 || C > 16384 || C % 4) return 0;
+  return (size_t)add_rmsnorm_bwd_blocks(N, C) * C * sizeof(float);
+}
+
+int ts2ts_add_rmsnorm_bwd(const void* dh, const float* dx_up, const float* x, const float* w, const float* rstd, float* dx, void* da,
+                          float* dw, void* workspace, size_t workspace_bytes, int64_t N, int C, void* stream) {
+  int r;
+  if ((r = check_rows(N))) return r;
+  if (C < 4 || C > 16384 || C % 4) return fail(-2, "C must be a multiple of 4 in 4..16384 (got %d)", C);
+  if (!dh || !x || !w || !rstd || !dx || !dw || !workspace) return fail(-3, "add_rmsnorm_bwd: null pointer");
+  if (!aligned(dh, 8) || !aligned(x, 16) || !aligned(w, 16) || !aligned(dx, 16) || (dx_up && !aligned(dx_up, 16)) || (da && !aligned(da, 8)) ||
+      !aligned(workspace, 16))
+    return fail(-5, "add_rmsnorm_bwd: misaligned pointer");
+  if (workspace_bytes < ts2ts_add_rmsnorm_bwd_workspace_bytes(N, C)) return fail(-4, "add_rmsnorm_bwd: workspace too small");
+  return launched(launch_add_rmsnorm_bwd(dh, dx_up, x, w, rstd, dx, da, dw, static_cast<float*>(workspace), (int)N, C,
+                                         static_cast<cudaStream_t>(stream)), "add_rmsnorm_bwd");
+}
+
+int ts2ts_rope_qk_inplace(void* qkv, const float* cos, const float* sin, int B, int T, int H, int D, float sign, void* stream) {
+  if (B <= 0 || T <= 0 || H <= 0 || T > kMaxT) return fail(-1, "B, T, H must be positive (T <= %d)", kMaxT);
+  if (D < 16 || D > 512 || D % 16) return fail(-2, "D must be a multiple of 16 in 16..512 (got %d)", D);
+  if (!qkv || !cos || !sin) return fail(-3, "rope_qk_inplace: null pointer");
+  if (!aligned(qkv, 16) || !aligned(cos, 16) || !aligned(sin, 16)) return fail(-5, "rope_qk_inplace: misaligned pointer");
+  if (sign != 1.f && sign != -1.f) return fail(-8, "sign must be +1 or -1");
+  return launched(launch_rope_qk(qkv, cos, sin, B, T, H, D, sign, static_cast<cudaStream_t>(stream)), "rope_qk");
+}
+
+int ts2ts_swiglu_fwd(const void* gu, void* act, int64_t N, int F, void* stream) {
+  int r;
+  if ((r = check_rows(N))) return r;
+  if (F < 8 || F % 8) return fail(-2, "F must be a positive multiple of 8 (got %d)", F);
+  if (!gu || !act) return fail(-3, "swiglu_fwd: null pointer");
+  if (!aligned(gu, 16) || !aligned(act, 16)) return fail(-5, "swiglu_fwd: misaligned pointer");
+  return launched(launch_swiglu_fwd(gu, act, N, F, static_cast<cudaStream_t>(stream)), "swiglu_fwd");
+}
+
+int ts2ts_swiglu_bwd(const void* gu, const void* dact, void* dgu, int64_t N, int F, void* stream) {
+  int r;
+  if ((r = check_rows(N))) return r;
+  if (F < 8 || F % 8) return fail(-2, "F must be a positive multiple of 8 (got %d)", F);
+  if (!gu || !dact || !dgu) return fail(-3, "swiglu_bwd: null pointer");
+  if (!aligned(gu, 16) || !aligned(dact, 16) || !aligned(dgu, 16)) return fail(-5, "swiglu_bwd: misaligned pointer");
+  return launched(launch_swiglu_bwd(gu, dact, dgu, N, F, static_cast<cudaStream_t>(stream)), "swiglu_bwd");
+}
+
+int ts2ts_ce_fwd(const void* logits, const int64_t* target, float* lse, float* loss, int64_t N, int V, void* stream) {
+  int r;
+  if ((r = check_rows(N))) return r;
+  if (V < 8 || V % 8) return fail(-2, "V must be a positive multiple of 8 (got %d)", V);
+  if (!logits || !target || !lse || !loss) return fail(-3, "ce_fwd: null pointer");
+  if (!aligned(logits, 16)) return fail(-5, "ce_fwd: misaligned pointer");
+  return launched(launch_ce_fwd(logits, target, lse, loss, (int)N, V, static_cast<cudaStream_t>(stream)), "ce_fwd");
+}
+
+int ts2ts_ce_bwd(void* logits, const int64_t* target, const float* lse, const float* gscale, float inv_n, int64_t N, int V,
+                 void* stream) {
+  int r;
+  if ((r = check_rows(N))) return r;
+  if (V < 8 || V % 8) return fail(-2, "V must be a positive multiple of 8 (got %d)", V);
+  if (!logits || !target || !lse || !gscale) return fail(-3, "ce_bwd: null pointer");
+  if (!aligned(logits, 16)) return fail(-5, "ce_bwd: misaligned pointer");
+  return launched(launch_ce_bwd(logits, target, lse, gscale, inv_n, (int)N, V, static_cast<cudaStream_t>(stream)), "ce_bwd");
+}

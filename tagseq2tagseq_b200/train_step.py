@@ -4,9 +4,11 @@ This is the scaling half of the benchmark: the call order of the reference's tra
 (model/modules/training_module.py:195-211: shift tokens, build the mask once, embed -> backbone -> norm -> logits ->
 cross-entropy) and its DDP settings (main.py:404-415: static graph, no unused parameters, 256 MB buckets), with a
 plain pre-norm decoder (RMSNorm, fused QKV, RoPE, SwiGLU) standing in for the reference's tunalab modules, which are
-not available.  The attention call inside every layer is `ts2ts::masked_attn`; the block plan is built once per
-micro-batch and shared by all layers, as the reference shares its BlockMask (block_mask_creator.py:132-139).
-Everything except the attention operator is ordinary PyTorch (cuBLAS GEMMs, fused AdamW): plumbing, not the product.
+not available.  Every layer calls the masked-attention kernels on the packed QKV projection (lm_fused.qkv_attention);
+the block plan is built once per micro-batch and shared by all layers, as the reference shares its BlockMask
+(block_mask_creator.py:132-139).  The GEMMs are cuBLAS through torch and the optimizer is torch's fused AdamW; the
+memory-bound pieces between them (residual add + RMSNorm, rotary embedding, SwiGLU, cross-entropy) are single-pass
+kernels of this library, as the reference's are fused modules.
 """
 from __future__ import annotations
 
@@ -19,8 +21,10 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from .attention import masked_attn
+from .lm_fused import add_rmsnorm, cross_entropy, qkv_attention, rope_half_tables, swiglu
 from .mask_spec import MaskSpec
+
+RMS_EPS = float(torch.finfo(torch.float32).eps)  # what nn.RMSNorm uses for fp32 input when eps is None
 
 
 @dataclass
@@ -66,6 +70,10 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 
 
 class Block(nn.Module):
+    """Pre-norm decoder layer.  It receives the residual stream ``x`` (fp32) and the branch output ``a`` (bf16) that
+    has not been added to it yet, so that the add fuses with the RMSNorm that follows; it returns the pair in the
+    same form: x <- x + a; x <- x + attn(norm(x)) is returned as (x, mlp branch output)."""
+
     def __init__(self, cfg: LMConfig):
         super().__init__()
         hd = cfg.n_heads * cfg.head_dim
@@ -77,17 +85,12 @@ class Block(nn.Module):
         self.gate_up = nn.Linear(cfg.d_model, 2 * cfg.mlp_hidden, bias=False)
         self.down = nn.Linear(cfg.mlp_hidden, cfg.d_model, bias=False)
 
-    def forward(self, x, mask: MaskSpec, cos, sin):
-        B, T, _ = x.shape
+    def forward(self, x, a, mask: MaskSpec, cos, sin):
         c = self.cfg
-        qkv = self.qkv(self.ln1(x)).view(B, T, 3, c.n_heads, c.head_dim)
-        qk = apply_rope(qkv[:, :, :2], cos, sin)                                # q and k rotated together, [B,T,2,H,D]
-        q, k, v = qk[:, :, 0].permute(0, 2, 1, 3), qk[:, :, 1].permute(0, 2, 1, 3), qkv[:, :, 2].permute(0, 2, 1, 3)  # [B,H,T,D] strided views
-        out, _ = masked_attn(q, k, v, mask.doc_ids, mask.link_bits, q_row_ids=mask.q_row_ids, kv_col_ids=mask.kv_col_ids,
-                             plan=mask.plan)                                      # x + attn(ln(x)), layer.py:32-35
-        x = x + self.proj(out.transpose(1, 2).reshape(B, T, c.n_heads * c.head_dim))
-        g, u = self.gate_up(self.ln2(x)).chunk(2, dim=-1)
-        return x + self.down(F.silu(g) * u)
+        x, h = add_rmsnorm(x, a, self.ln1.weight, RMS_EPS)
+        attn = qkv_attention(self.qkv(h), cos, sin, mask, c.n_heads, c.head_dim)   # rotary + masked attention, layer.py:32-35
+        x, h = add_rmsnorm(x, self.proj(attn), self.ln2.weight, RMS_EPS)
+        return x, self.down(swiglu(self.gate_up(h)))
 
 
 class DecoderLM(nn.Module):
@@ -103,16 +106,20 @@ class DecoderLM(nn.Module):
                 nn.init.normal_(p, std=0.02)
 
     def forward(self, tokens: torch.Tensor, mask: MaskSpec) -> torch.Tensor:
-        """tokens int64 [B, T+1]; returns the mean next-token cross-entropy (training_module.py:195-211)."""
+        """tokens int64 [B, T+1]; returns the mean next-token cross-entropy (training_module.py:195-211).  Runs under
+        bf16 autocast: the linear layers compute in bf16, the residual stream, norms, rotary angles and the loss in fp32."""
         inp, tgt = tokens[:, :-1], tokens[:, 1:]
         T = inp.shape[1]
-        x = self.embed(inp)
-        cos, sin = (t.to(x.dtype if not torch.is_autocast_enabled() else torch.get_autocast_dtype("cuda"))[None, :, None, None, :]
-                    for t in rope_tables(T, self.cfg.head_dim, self.cfg.rope_base, inp.device))
+        x = self.embed(inp).float()
+        cos, sin = rope_half_tables(T, self.cfg.head_dim, self.cfg.rope_base, inp.device)
+        a = None
         for blk in self.blocks:
-            x = blk(x, mask, cos, sin)
-        logits = self.head(self.norm(x))
-        return F.cross_entropy(logits.float().view(-1, logits.shape[-1]), tgt.reshape(-1))
+            x, a = blk(x, a, mask, cos, sin)
+        _, h = add_rmsnorm(x, a, self.norm.weight, RMS_EPS)
+        logits = self.head(h)
+        if logits.dtype != torch.bfloat16:
+            logits = logits.to(torch.bfloat16)
+        return cross_entropy(logits.view(-1, logits.shape[-1]), tgt.reshape(-1))
 
 
 class TrainStep:

@@ -9,9 +9,12 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def declared_symbols():
-    text = open(os.path.join(ROOT, "include", "ts2ts_attn.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(ts2ts_\w+)\s*\(", text)))
+    names = set()
+    for header in ("ts2ts_attn.h", "ts2ts_lm.h"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        names |= set(re.findall(r"\b(ts2ts_\w+)\s*\(", text))
+    return sorted(names)
 
 
 def test_every_declared_symbol_is_exported_and_bound():
@@ -19,7 +22,7 @@ def test_every_declared_symbol_is_exported_and_bound():
     assert len(names) >= 9
     handle = ctypes.CDLL(build.build_library())
     for n in names:
-        assert hasattr(handle, n), f"{n} declared in include/ts2ts_attn.h but not exported"
+        assert hasattr(handle, n), f"{n} declared in include/ but not exported"
     assert sorted(_lib.SYMBOLS) == names
 
 
