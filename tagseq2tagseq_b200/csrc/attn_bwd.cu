@@ -44,9 +44,10 @@
 #endif
 
 #ifndef TS2TS_BWD_GROUP_MB
-// Q/dO bytes of the heads whose CTAs are interleaved in the launch order.  Measured on the 32k masks: 64 MB (3 heads)
-// is 2 % faster than one head at a time; 136 MB is 4 % slower and all heads 10 % slower (Q / dO fall out of L2).
-#define TS2TS_BWD_GROUP_MB 64
+// Q/dO bytes of the heads whose CTAs are interleaved in the launch order.  Measured on the 32k masks in the
+// seconds-long benchmark loop: 32 MB (one head at 32k, three at 16k) gives the best whole-step rate, 2-3 % above 64 MB
+// and 16 MB; 136 MB is 4 % slower and all heads 10 % slower (Q / dO fall out of L2).
+#define TS2TS_BWD_GROUP_MB 32
 #endif
 
 namespace ts2ts {
@@ -842,7 +843,7 @@ static int launch_bwd_t(const void* q, const void* k, const void* v, const void*
   p.dk = static_cast<__nv_bfloat16*>(dk); p.dv = static_cast<__nv_bfloat16*>(dv);
   for (int i = 0; i < 3; ++i) { p.dk_s[i] = sdk[i]; p.dv_s[i] = sdv[i]; }
   p.H = H; p.Tp = Tp; p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
-  {  // heads per group: their Q and dO (2 x T x D bf16 each) should fit in about half of the 126 MB L2
+  {  // heads per group: their Q and dO (2 x T x D bf16 each) stay within TS2TS_BWD_GROUP_MB, a quarter of the L2
     const long long qdo_bytes = 4ll * T * D;
     long long g = (static_cast<long long>(TS2TS_BWD_GROUP_MB) << 20) / (qdo_bytes > 0 ? qdo_bytes : 1);
     p.head_group = (int)(g < 1 ? 1 : (g > H ? H : g));
