@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import ctypes
+import gc
 import json
 import os
 import statistics
@@ -575,13 +576,17 @@ def run_train(args, rank, world, device, which: str, steps: int, warmup: int, bo
         batches = []
         for i in mine:
             batches.append((torch.randint(0, cfg.vocab, (1, t_len + 1), generator=g).to(device), to_spec(pool[i]), pool[i].unmasked_pairs()))
-        for i in range(warmup):
+        for i in range(max(warmup, n_packs)):  # every batch of the schedule once before the clock starts
             tok, spec, _ = batches[i % n_packs]
             spec._block_map = None
             loss = ts.step(tok, spec)
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize(device)
+        # The step is 30 ms of kernels behind 15-20 ms of host work per rank: a full Python garbage collection in the
+        # middle of the timed steps (tens of ms with this many live objects) would be billed to the GPU.
+        gc.collect()
+        gc.disable()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ev0.record()
         flops = 0.0
@@ -594,6 +599,7 @@ def run_train(args, rank, world, device, which: str, steps: int, warmup: int, bo
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize(device)
+        gc.enable()
         my_ms = ev0.elapsed_time(ev1)
         (ms,), (tot_flops, tot_tokens) = aggregate([my_ms], [flops, float(t_len * steps)], device)
         res = {"value": tot_tokens / (ms * 1e-3), "ms_per_step": ms / steps,

@@ -5,6 +5,7 @@ CUDA only: there is no CPU path.
 """
 from __future__ import annotations
 
+import contextlib
 import math
 from typing import Optional, Tuple
 
@@ -16,8 +17,17 @@ from .mask_spec import MaskSpec
 __all__ = ["add_rmsnorm", "qkv_attention", "swiglu", "cross_entropy", "rope_half_tables"]
 
 
+_NO_GUARD = contextlib.nullcontext()
+
+
 def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _on_device(t: torch.Tensor):
+    """Device guard for the launches; free when the tensor already lives on the current device (the usual case: the
+    training step issues a few hundred of these calls per step from Python)."""
+    return _NO_GUARD if t.device.index == torch.cuda.current_device() else torch.cuda.device(t.device)
 
 
 def _need_cuda(*ts):
@@ -39,7 +49,7 @@ class _AddRMSNorm(torch.autograd.Function):
         x_out = torch.empty_like(x_in)
         h = torch.empty(x_in.shape, dtype=torch.bfloat16, device=x_in.device)
         rstd = torch.empty(N, dtype=torch.float32, device=x_in.device)
-        with torch.cuda.device(x_in.device):
+        with _on_device(x_in):
             code = _lib.lib().ts2ts_add_rmsnorm_fwd(x_in.data_ptr(), None if a is None else a.data_ptr(), w.data_ptr(), x_out.data_ptr(),
                                                     h.data_ptr(), rstd.data_ptr(), N, C, eps, _stream(x_in))
         _lib.check(code, "ts2ts_add_rmsnorm_fwd")
@@ -61,7 +71,7 @@ class _AddRMSNorm(torch.autograd.Function):
         dw = torch.zeros_like(w)
         L = _lib.lib()
         ws = torch.empty(L.ts2ts_add_rmsnorm_bwd_workspace_bytes(N, C), dtype=torch.uint8, device=x.device)
-        with torch.cuda.device(x.device):
+        with _on_device(x):
             code = L.ts2ts_add_rmsnorm_bwd(dh.data_ptr(), None if dx_up is None else dx_up.data_ptr(), x.data_ptr(), w.data_ptr(),
                                            rstd.data_ptr(), dx.data_ptr(), None if da is None else da.data_ptr(), dw.data_ptr(),
                                            ws.data_ptr(), ws.numel(), N, C, _stream(x))
@@ -101,7 +111,7 @@ class _QKVAttention(torch.autograd.Function):
             raise ValueError("qkv_attention: last dimension must be 3 * n_heads * head_dim")
         L = _lib.lib()
         st = _stream(qkv)
-        with torch.cuda.device(qkv.device):
+        with _on_device(qkv):
             _lib.check(L.ts2ts_rope_qk_inplace(qkv.data_ptr(), cos.data_ptr(), sin.data_ptr(), B, T, H, D, 1.0, st), "ts2ts_rope_qk_inplace")
         ctx.mark_dirty(qkv)
         packed = qkv.view(B, T, 3, H, D)
@@ -112,7 +122,7 @@ class _QKVAttention(torch.autograd.Function):
         doc, link, rows, cols, plan = mask.doc_ids, mask.link_bits, mask.q_row_ids, mask.kv_col_ids, mask.plan
         R, W = (0, 0) if link is None else (link.shape[1], link.shape[2])
         scale = 1.0 / math.sqrt(D)
-        with torch.cuda.device(qkv.device):
+        with _on_device(qkv):
             code = L.ts2ts_attn_fwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), _strides_bhtd(q), _strides_bhtd(k), _strides_bhtd(v), B, H, T, D,
                                     scale, doc.data_ptr(), None if rows is None else rows.data_ptr(), None if cols is None else cols.data_ptr(),
                                     None if link is None else link.data_ptr(), R, W, plan.data_ptr(), plan.numel(), out_v.data_ptr(),
@@ -139,7 +149,7 @@ class _QKVAttention(torch.autograd.Function):
         ws = torch.empty(L.ts2ts_attn_bwd_workspace_bytes(B, H, T, D), dtype=torch.uint8, device=qkv.device)
         doc, link, rows, cols, plan = mask.doc_ids, mask.link_bits, mask.q_row_ids, mask.kv_col_ids, mask.plan
         R, W = (0, 0) if link is None else (link.shape[1], link.shape[2])
-        with torch.cuda.device(qkv.device):
+        with _on_device(qkv):
             code = L.ts2ts_attn_bwd(q.data_ptr(), k.data_ptr(), v.data_ptr(), out_v.data_ptr(), dout_v.data_ptr(), lse.data_ptr(),
                                     _strides_bhtd(q), _strides_bhtd(k), _strides_bhtd(v), _strides_bhtd(out_v), _strides_bhtd(dout_v), B, H, T, D,
                                     ctx.scale, doc.data_ptr(), None if rows is None else rows.data_ptr(),
@@ -169,7 +179,7 @@ class _SwiGLU(torch.autograd.Function):
         F = gu.shape[-1] // 2
         N = gu.numel() // (2 * F)
         act = torch.empty(gu.shape[:-1] + (F,), dtype=torch.bfloat16, device=gu.device)
-        with torch.cuda.device(gu.device):
+        with _on_device(gu):
             _lib.check(_lib.lib().ts2ts_swiglu_fwd(gu.data_ptr(), act.data_ptr(), N, F, _stream(gu)), "ts2ts_swiglu_fwd")
         ctx.save_for_backward(gu)
         return act
@@ -181,7 +191,7 @@ class _SwiGLU(torch.autograd.Function):
         N = gu.numel() // (2 * F)
         dact = dact.contiguous()
         dgu = torch.empty_like(gu)
-        with torch.cuda.device(gu.device):
+        with _on_device(gu):
             _lib.check(_lib.lib().ts2ts_swiglu_bwd(gu.data_ptr(), dact.data_ptr(), dgu.data_ptr(), N, F, _stream(gu)), "ts2ts_swiglu_bwd")
         return dgu
 
@@ -201,7 +211,7 @@ class _CrossEntropy(torch.autograd.Function):
         N, V = logits.shape
         lse = torch.empty(N, dtype=torch.float32, device=logits.device)
         loss = torch.empty(N, dtype=torch.float32, device=logits.device)
-        with torch.cuda.device(logits.device):
+        with _on_device(logits):
             _lib.check(_lib.lib().ts2ts_ce_fwd(logits.data_ptr(), target.data_ptr(), lse.data_ptr(), loss.data_ptr(), N, V, _stream(logits)),
                        "ts2ts_ce_fwd")
         ctx.save_for_backward(logits, target, lse)
@@ -213,7 +223,7 @@ class _CrossEntropy(torch.autograd.Function):
         N, V = logits.shape
         g = g.reshape(1).to(torch.float32).contiguous()
         # the logits are not needed again: their buffer becomes the gradient
-        with torch.cuda.device(logits.device):
+        with _on_device(logits):
             _lib.check(_lib.lib().ts2ts_ce_bwd(logits.data_ptr(), target.data_ptr(), lse.data_ptr(), g.data_ptr(), 1.0 / N, N, V, _stream(logits)),
                        "ts2ts_ce_bwd")
         return logits, None
