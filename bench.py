@@ -564,6 +564,8 @@ def run_train(args, rank, world, device, which: str, steps: int, warmup: int, bo
         for pk in pool:
             sp = to_spec(pk)
             costs.append(float(tile_cost(sp.doc_ids, sp.link_bits)))
+        del sp
+        torch.cuda.empty_cache()  # the block maps with explicit lists leave odd-sized cached blocks behind
     peak_tf, _, kind = measured_peaks()
 
     def measure(schedule_name):
