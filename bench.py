@@ -549,7 +549,7 @@ def run_train(args, rank, world, device, which: str, steps: int, warmup: int, bo
     from tagseq2tagseq_b200.replicas import aggregate, rank_seed, schedule_packs, tile_cost
     from tagseq2tagseq_b200.train_step import TrainStep, config4, config5, train_flops_per_step
     cfg, t_len, base = (config4(), 16384, 1004) if which == "train4" else (config5(), 32768, 1005)
-    ts = TrainStep(cfg, device, world, bucket_cap_mb=args.bucket_mb)
+    ts = TrainStep(cfg, device, world, bucket_cap_mb=args.bucket_mb, bf16_grads=not args.fp32_buckets)
     n_packs = 4  # steps in the pool
     make = (lambda sd: synth.config2_pack(sd)) if which == "train4" else (lambda sd: synth.config5_pack(sd))
     pool = [make(rank_seed(base, r, i)) for i in range(n_packs) for r in range(world)]
@@ -931,6 +931,7 @@ def main():
                          "flex_gpu: PyTorch FlexAttention (the reference's GPU path) on the same inputs, single GPU.")
     ap.add_argument("--no-balance", action="store_true", help="training step: keep the seed order of packs instead of the density-aware schedule")
     ap.add_argument("--bucket-mb", type=int, default=256, help="training step: DDP bucket size in MB (the reference uses 256, main.py:414)")
+    ap.add_argument("--fp32-buckets", action="store_true", help="training step: all-reduce fp32 gradient buckets (default: bf16-compressed)")
     ap.add_argument("--no-train", action="store_true", help="skip the short training-step measurement appended to the 32k line")
     ap.add_argument("--workload", default="32k", choices=["32k", "16k", "train4", "train5"],
                     help="32k: the headline mask sweep (default).  16k: B=1, T=16384, H=16, cross_doc_link p=0.15 "
