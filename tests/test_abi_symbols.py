@@ -65,3 +65,23 @@ def test_link_scan_argument_rejection_needs_no_gpu():
     assert call(flags=None) == -6 and call(win=-1) == -6
     assert call(sbytes=16) == -9
     assert call(links=None) == -3
+
+
+def test_decoder_layer_entry_points_reject_bad_arguments_without_a_gpu():
+    L = _lib.lib()
+    assert L.ts2ts_add_rmsnorm_bwd_workspace_bytes(0, 768) == 0 and L.ts2ts_add_rmsnorm_bwd_workspace_bytes(16, 6) == 0
+    ws = L.ts2ts_add_rmsnorm_bwd_workspace_bytes(16384, 768)
+    assert ws % (768 * 4) == 0 and 0 < ws <= 16384 * 768 * 4
+    assert L.ts2ts_add_rmsnorm_bwd_workspace_bytes(3, 768) == 3 * 768 * 4          # never more partial rows than rows
+    assert L.ts2ts_add_rmsnorm_fwd(16, None, 16, 16, 16, 16, 0, 768, 1e-6, None) == -1
+    assert L.ts2ts_add_rmsnorm_fwd(16, None, 16, 16, 16, 16, 8, 770, 1e-6, None) == -2
+    assert L.ts2ts_add_rmsnorm_fwd(None, None, 16, 16, 16, 16, 8, 768, 1e-6, None) == -3
+    assert L.ts2ts_add_rmsnorm_fwd(20, None, 16, 16, 16, 16, 8, 768, 1e-6, None) == -5
+    assert L.ts2ts_add_rmsnorm_bwd(16, None, 16, 16, 16, 16, None, 16, 16, 8, 16384, 768, None) == -4
+    assert b"workspace" in L.ts2ts_last_error_string()
+    assert L.ts2ts_rope_qk_inplace(16, 16, 16, 1, 128, 2, 40, 1.0, None) == -2
+    assert L.ts2ts_rope_qk_inplace(16, 16, 16, 1, 128, 2, 64, 0.5, None) == -8
+    assert L.ts2ts_swiglu_fwd(16, 16, 8, 12, None) == -2
+    assert L.ts2ts_swiglu_bwd(16, None, 16, 8, 16, None) == -3
+    assert L.ts2ts_ce_fwd(16, 16, 16, 16, 8, 50300, None) == -2
+    assert L.ts2ts_ce_bwd(18, 16, 16, 16, 0.5, 8, 512, None) == -5

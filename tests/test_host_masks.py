@@ -156,3 +156,18 @@ def test_grant_segments_describe_the_same_mask_as_grant_classes(seed):
     a = _dense_from_classes(row, col, link, t)
     b = _dense_from_classes(_expand_segments(qb, qi, t), _expand_segments(kb, ki, t), link2, t)
     assert np.array_equal(a, b)
+
+
+def test_decoder_layer_wrappers_refuse_cpu_tensors():
+    import pytest
+    import torch
+    from tagseq2tagseq_b200 import lm_fused
+    x = torch.zeros(4, 128)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        lm_fused.add_rmsnorm(x, None, torch.ones(128), 1e-6)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        lm_fused.swiglu(torch.zeros(4, 256, dtype=torch.bfloat16))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        lm_fused.cross_entropy(torch.zeros(4, 512, dtype=torch.bfloat16), torch.zeros(4, dtype=torch.int64))
+    cos, sin = lm_fused.rope_half_tables(5, 64, 10000.0, "cpu")
+    assert cos.shape == (5, 32) and sin.shape == (5, 32) and float(cos[0, 0]) == 1.0 and float(sin[0, 0]) == 0.0
