@@ -269,6 +269,7 @@ __global__ void ce_fwd_kernel(const __nv_bfloat16* __restrict__ logits, const in
 #pragma unroll
     for (int i = 1; i < 8; ++i) mx = fmaxf(mx, f[i]);
     const float m_new = fmaxf(m, mx);
+    if (m_new == -CUDART_INF_F) continue;  // nothing but -inf so far: contributes nothing, and -inf - -inf is no number
     float add = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) add += __expf(f[i] - m_new);
